@@ -13,6 +13,7 @@
 #include "gemm_tc.h"
 #include "kernels.h"
 #include "runtime.h"
+#include "bindings_hybrid.h"
 #include "tma_host.h"
 
 namespace {
@@ -114,7 +115,9 @@ TcChoice pick_tc_tile(int64_t M, int64_t N, bool a_mn, bool b_mn, bool f32_out) 
   double best_s = -1.0;
   for (const Cand& c : all) {
     if (a_mn && !((c.cg == 1 && c.bn != 192) || (c.cg == 2 && c.bn == 256))) continue;      // instantiated wgrad shapes
-    if (f32_out && !a_mn) continue;
+    // float32 results: weight gradients (MN x MN) and forward linears whose consumer wants the unrounded sum (K x K)
+    if (f32_out && !((a_mn && b_mn) || (!a_mn && !b_mn))) continue;
+    if (f32_out && !((c.cg == 1 && c.bn != 192) || (c.cg == 2 && c.bn == 256))) continue;
     const int64_t tm = c.cg * 128;
     const int64_t num_m = (M + tm - 1) / tm, num_n = (N + c.bn - 1) / c.bn, tiles = num_m * num_n;
     const int64_t units = sms / c.cg, waves = (tiles + units - 1) / units;
@@ -1051,4 +1054,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("master") = py::none());
   m.def("allreduce_sum", &allreduce_sum);
   nrl::bind_runtime(m);
+  nrl::bind_hybrid(m);
 }

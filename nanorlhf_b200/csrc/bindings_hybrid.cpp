@@ -1,0 +1,194 @@
+// Tensor validation + stream forwarding for the hybrid-decoder kernels; the launch API is hybrid_kernels.h.
+#include "bindings_hybrid.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "hybrid_kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline void check(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e)); }
+
+inline const float* f32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32, name, " must be a CUDA float tensor");
+  TORCH_CHECK(t.dim() == 0 || t.stride(-1) == 1, name, " must have unit inner stride");
+  return t.data_ptr<float>();
+}
+inline float* f32w(Tensor& t, const char* name) { return const_cast<float*>(f32(t, name)); }
+inline const int* i32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be a contiguous CUDA int32 tensor");
+  return t.data_ptr<int>();
+}
+// typed operand: float or bf16 with unit inner stride; returns is-float
+inline int typed(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && (t.scalar_type() == torch::kFloat32 || t.scalar_type() == torch::kBFloat16), name,
+              " must be a CUDA float or bf16 tensor");
+  TORCH_CHECK(t.stride(-1) == 1, name, " must have unit inner stride");
+  return t.scalar_type() == torch::kFloat32 ? 1 : 0;
+}
+
+void embed_pos(const Tensor& embed, const Tensor& pos_table, const Tensor& tok, const Tensor& pos, Tensor out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  const int wf = typed(embed, "embed");
+  TORCH_CHECK(typed(pos_table, "pos_table") == wf && embed.is_contiguous() && pos_table.is_contiguous(), "embed_pos: tables");
+  const int T = static_cast<int>(tok.numel()), W = static_cast<int>(embed.size(1));
+  TORCH_CHECK(out.is_contiguous() && out.size(0) >= T && out.size(1) == W && pos_table.size(1) == W, "embed_pos: shapes");
+  check(nrl_embed_pos(embed.data_ptr(), pos_table.data_ptr(), wf, i32(tok, "tok"), i32(pos, "pos"), f32w(out, "out"), T, W, cur_stream()),
+        "embed_pos");
+}
+
+void stream_norm(Tensor results, int64_t i, const c10::optional<Tensor>& o, const c10::optional<Tensor>& xprev,
+                 const c10::optional<Tensor>& dw, const Tensor& g, double eps, Tensor xcur, Tensor h, int64_t T) {
+  c10::cuda::CUDAGuard guard(h.device());
+  TORCH_CHECK(results.dim() == 3 && results.stride(2) == 1 && results.stride(1) == results.size(2), "stream_norm: results [n, cap, W]");
+  const int W = static_cast<int>(results.size(2));
+  TORCH_CHECK(i >= 0 && i < results.size(0) && T <= results.size(1), "stream_norm: index");
+  TORCH_CHECK(xcur.is_contiguous() && xcur.size(-1) == W && h.is_contiguous() && h.size(-1) == W, "stream_norm: outputs");
+  TORCH_CHECK(o.has_value() == xprev.has_value(), "stream_norm: o and xprev go together");
+  if (o.has_value()) TORCH_CHECK(o->is_contiguous() && xprev->is_contiguous() && o->size(-1) == W, "stream_norm: o / xprev");
+  if (dw.has_value()) TORCH_CHECK(dw->numel() == i + 1, "stream_norm: one depth weight per result");
+  check(nrl_stream_norm(f32w(results, "results"), results.stride(0), static_cast<int>(i), o.has_value() ? f32(*o, "o") : nullptr,
+                        xprev.has_value() ? f32(*xprev, "xprev") : nullptr, dw.has_value() ? f32(*dw, "dw") : nullptr, f32(g, "g"),
+                        static_cast<float>(eps), f32w(xcur, "xcur"), h.data_ptr(), typed(h, "h"), static_cast<int>(T), W, cur_stream()),
+        "stream_norm");
+}
+
+void act_cols(const Tensor& in, Tensor out, int64_t act) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(in.dim() == 2 && out.dim() == 2 && in.size(0) == out.size(0) && in.size(1) == out.size(1), "act_cols: shapes");
+  check(nrl_act_cols(f32(in, "in"), in.stride(0), out.data_ptr(), out.stride(0), typed(out, "out"), static_cast<int>(act),
+                     static_cast<int>(in.size(0)), static_cast<int>(in.size(1)), cur_stream()),
+        "act_cols");
+}
+
+void gated_part_rmsnorm(const Tensor& y, const Tensor& gate, const Tensor& w, int64_t part, int64_t gate_act, bool gate_first,
+                        double eps, double scale, Tensor out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(y.dim() == 2 && gate.dim() == 2 && out.dim() == 2 && gate.size(1) == y.size(1) && out.size(1) == y.size(1) &&
+                  gate.size(0) == y.size(0) && out.size(0) == y.size(0), "gated_part_rmsnorm: shapes");
+  const bool shared = w.numel() == part;
+  TORCH_CHECK(shared || w.numel() == y.size(1), "gated_part_rmsnorm: weight of one part or of all columns");
+  check(nrl_gated_part_rmsnorm(f32(y, "y"), y.stride(0), f32(gate, "gate"), gate.stride(0), f32(w, "w"), shared ? 1 : 0,
+                               static_cast<int>(part), static_cast<int>(gate_act), gate_first ? 1 : 0, static_cast<float>(eps),
+                               static_cast<float>(scale), out.data_ptr(), out.stride(0), typed(out, "out"),
+                               static_cast<int>(y.size(0)), static_cast<int>(y.size(1)), cur_stream()),
+        "gated_part_rmsnorm");
+}
+
+void causal_conv(const Tensor& in, const Tensor& w, const c10::optional<Tensor>& bias, Tensor state, Tensor out, const Tensor& cu,
+                 const Tensor& tok_entry, const Tensor& start, const Tensor& state_slot) {
+  c10::cuda::CUDAGuard guard(out.device());
+  const int T = static_cast<int>(in.size(0)), C = static_cast<int>(in.size(1)), taps = static_cast<int>(w.size(1));
+  const int E = static_cast<int>(start.numel());
+  TORCH_CHECK(in.dim() == 2 && out.dim() == 2 && out.size(0) == T && out.size(1) == C && w.is_contiguous() && w.size(0) == C,
+              "causal_conv: shapes");
+  TORCH_CHECK(state.is_contiguous() && state.dim() == 3 && state.size(1) == taps - 1 && state.size(2) == C, "causal_conv: state [slots, taps-1, C]");
+  TORCH_CHECK(cu.numel() == E + 1 && tok_entry.numel() >= T && state_slot.numel() == E, "causal_conv: plan");
+  if (bias.has_value()) TORCH_CHECK(bias->numel() == C, "causal_conv: bias");
+  check(nrl_causal_conv(f32(in, "in"), in.stride(0), f32(w, "w"), bias.has_value() ? f32(*bias, "bias") : nullptr, f32(state, "state"),
+                        f32w(out, "out"), out.stride(0), i32(cu, "cu"), i32(tok_entry, "tok_entry"), i32(start, "start"),
+                        i32(state_slot, "state_slot"), T, C, taps, cur_stream()),
+        "causal_conv");
+  check(nrl_causal_conv_carry(f32(in, "in"), in.stride(0), f32w(state, "state"), i32(cu, "cu"), i32(start, "start"),
+                              i32(state_slot, "state_slot"), E, C, taps, cur_stream()),
+        "causal_conv_carry");
+}
+
+void ssd_scan(const Tensor& xbc, int64_t col_b, int64_t col_c, const Tensor& dt_raw, const Tensor& dt_bias, const Tensor& A_log,
+              const Tensor& Dskip, Tensor state, Tensor y, const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t groups) {
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(state.dim() == 4 && state.is_contiguous(), "ssd_scan: state [slots, heads, N, P]");
+  const int heads = static_cast<int>(state.size(1)), N = static_cast<int>(state.size(2)), P = static_cast<int>(state.size(3));
+  const int E = static_cast<int>(start.numel());
+  TORCH_CHECK(xbc.dim() == 2 && dt_raw.dim() == 2 && dt_raw.size(1) == heads && y.is_contiguous() && y.size(-1) == heads * P &&
+                  y.size(0) >= xbc.size(0), "ssd_scan: shapes");
+  TORCH_CHECK(col_b >= heads * P && col_c + groups * N <= xbc.size(1) && dt_bias.numel() == heads && A_log.numel() == heads &&
+                  Dskip.numel() == heads, "ssd_scan: columns / per-head vectors");
+  check(nrl_ssd_scan(f32(xbc, "xbc"), xbc.stride(0), static_cast<int>(col_b), static_cast<int>(col_c), f32(dt_raw, "dt_raw"),
+                     dt_raw.stride(0), f32(dt_bias, "dt_bias"), f32(A_log, "A_log"), f32(Dskip, "D"), f32w(state, "state"), f32w(y, "y"),
+                     i32(cu, "cu"), i32(start, "start"), i32(state_slot, "state_slot"), E, heads, static_cast<int>(groups), N, P,
+                     cur_stream()),
+        "ssd_scan");
+}
+
+void delta_prep(Tensor qkv, int64_t col_k, const Tensor& b_raw, const Tensor& a_raw, const Tensor& dt_bias, const Tensor& A_log,
+                Tensor beta, Tensor decay, int64_t kv_heads, int64_t D, bool per_channel) {
+  c10::cuda::CUDAGuard guard(qkv.device());
+  const int T = static_cast<int>(qkv.size(0)), heads = static_cast<int>(A_log.numel());
+  TORCH_CHECK(dt_bias.numel() == (per_channel ? static_cast<int64_t>(heads) * D : heads), "delta_prep: dt_bias per head or per head and key channel");
+  TORCH_CHECK(b_raw.dim() == 2 && b_raw.size(1) == heads && a_raw.dim() == 2 && a_raw.size(1) == dt_bias.numel() && beta.is_contiguous() &&
+                  decay.is_contiguous() && beta.numel() >= static_cast<int64_t>(T) * heads &&
+                  decay.numel() >= static_cast<int64_t>(T) * dt_bias.numel(), "delta_prep: shapes");
+  check(nrl_delta_prep(f32w(qkv, "qkv"), qkv.stride(0), static_cast<int>(col_k), f32(b_raw, "b_raw"), b_raw.stride(0), f32(a_raw, "a_raw"),
+                       a_raw.stride(0), f32(dt_bias, "dt_bias"), f32(A_log, "A_log"), f32w(beta, "beta"), f32w(decay, "decay"), T, heads,
+                       static_cast<int>(kv_heads), static_cast<int>(D), per_channel ? 1 : 0, cur_stream()),
+        "delta_prep");
+}
+
+void delta_scan(const Tensor& qkv, int64_t col_k, int64_t col_v, const Tensor& beta, const Tensor& decay, Tensor state, Tensor o,
+                const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t kv_heads, bool per_channel) {
+  c10::cuda::CUDAGuard guard(o.device());
+  TORCH_CHECK(state.dim() == 4 && state.is_contiguous(), "delta_scan: state [slots, heads, D, Dv]");
+  const int heads = static_cast<int>(state.size(1)), D = static_cast<int>(state.size(2)), Dv = static_cast<int>(state.size(3));
+  const int E = static_cast<int>(start.numel());
+  TORCH_CHECK(qkv.dim() == 2 && col_v + heads * Dv <= qkv.size(1) && o.is_contiguous() && o.size(-1) == heads * Dv, "delta_scan: shapes");
+  check(nrl_delta_scan(f32(qkv, "qkv"), qkv.stride(0), static_cast<int>(col_k), static_cast<int>(col_v), f32(beta, "beta"),
+                       f32(decay, "decay"), f32w(state, "state"), f32w(o, "o"), i32(cu, "cu"), i32(start, "start"),
+                       i32(state_slot, "state_slot"), E, heads, static_cast<int>(kv_heads), D, Dv, per_channel ? 1 : 0, cur_stream()),
+        "delta_scan");
+}
+
+void qknorm_kv_write(Tensor q, const Tensor& k, const Tensor& v, const Tensor& qw, const Tensor& kw, double eps, Tensor k_cache,
+                     Tensor v_cache, const Tensor& kv_slot) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "qknorm_kv_write: caches");
+  const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
+  const int Dv = static_cast<int>(v_cache.size(3));
+  const int T = static_cast<int>(q.size(0)), Hq = static_cast<int>(q.size(1) / D);
+  TORCH_CHECK(q.size(1) == static_cast<int64_t>(Hq) * D && k.size(1) == static_cast<int64_t>(Hkv) * D &&
+                  v.size(1) == static_cast<int64_t>(Hkv) * Dv && qw.numel() == D && kw.numel() == D && kv_slot.numel() >= T,
+              "qknorm_kv_write: shapes");
+  const int cf = typed(k_cache, "k_cache");
+  TORCH_CHECK(typed(v_cache, "v_cache") == cf, "qknorm_kv_write: cache types differ");
+  check(nrl_qknorm_kv_write(f32w(q, "q"), q.stride(0), f32(k, "k"), k.stride(0), f32(v, "v"), v.stride(0), f32(qw, "qw"), f32(kw, "kw"),
+                            static_cast<float>(eps), k_cache.data_ptr(), v_cache.data_ptr(), cf, i32(kv_slot, "kv_slot"), T, Hq, Hkv, D,
+                            Dv, page, cur_stream()),
+        "qknorm_kv_write");
+}
+
+void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table, const Tensor& tok_entry,
+                      const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
+  const int Dv = static_cast<int>(v_cache.size(3));
+  const int T = static_cast<int>(q.size(0)), Hq = static_cast<int>(q.size(1) / D);
+  TORCH_CHECK(block_table.dim() == 2 && out.dim() == 2 && out.size(0) == T && out.size(1) == static_cast<int64_t>(Hq) * Dv,
+              "window_attention: shapes");
+  check(nrl_window_attention(f32(q, "q"), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
+                             i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
+                             i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
+                             out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, cur_stream()),
+        "window_attention");
+}
+
+}  // namespace
+
+namespace nrl {
+void bind_hybrid(pybind11::module_& m) {
+  m.def("embed_pos", &embed_pos, "x0 = embed[tok] + pos_table[pos] (float)");
+  m.def("stream_norm", &stream_norm, "close a layer, form the depth-weighted stream and its single-gain RMS norm");
+  m.def("act_cols", &act_cols, "typed out = act(float in): 0 copy, 1 relu^2");
+  m.def("gated_part_rmsnorm", &gated_part_rmsnorm, "part-wise RMS norm with a silu / sigmoid gate before or after it");
+  m.def("causal_conv", &causal_conv, "depthwise causal convolution + silu with taps carried per state slot");
+  m.def("ssd_scan", &ssd_scan, "state-space scan with a scalar decay per head, state carried per slot");
+  m.def("delta_prep", &delta_prep, "unit q / k, beta and decays of the gated delta rule");
+  m.def("delta_scan", &delta_scan, "gated delta rule scan, state carried per slot");
+  m.def("qknorm_kv_write", &qknorm_kv_write, "per-head RMS norm of q (in place) and k (into the paged cache), v into the cache");
+  m.def("window_attention", &window_attention, "sliding-window attention over the paged cache");
+}
+}  // namespace nrl

@@ -22,8 +22,10 @@ OBJ = os.path.join(HERE, "build")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 CU_SOURCES = ["gemm_sm100.cu", "gemm_sm100_2cta.cu", "gemm_tc.cu", "elementwise.cu", "rl_kernels.cu", "sampling.cu", "attention_decode.cu", "attention_decode_fp8.cu", "rope_kv.cu", "attention_fwd_tc.cu", "attention_bwd_tc.cu",
-              "attention_varlen.cu", "comm.cu", "quant.cu"]
-CPP_SOURCES = ["bindings.cpp", "runtime.cpp"]
+              "attention_varlen.cu", "comm.cu", "quant.cu", "stream_ops.cu", "recurrent.cu", "attention_window.cu"]
+CPP_SOURCES = ["bindings.cpp", "runtime.cpp", "bindings_hybrid.cpp"]
+# kernels of the float32 serving mode: IEEE division / sqrt / exp (no --use_fast_math)
+PRECISE_SOURCES = {"stream_ops.cu", "recurrent.cu", "attention_window.cu"}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 if os.environ.get("NRL_ATTN_PROFILE") == "1":       # cycle accounting build of attention_fwd_tc.cu (bench/attn_prof.py)
@@ -65,9 +67,10 @@ def build(verbose: bool = True, force: bool = False) -> str:
             continue
         o = os.path.join(OBJ, src + ".o")
         objs.append(o)
-        st = _stamp(p, " ".join(NVCC_FLAGS))
+        flags = [f for f in NVCC_FLAGS if f != "--use_fast_math"] if src in PRECISE_SOURCES else NVCC_FLAGS
+        st = _stamp(p, " ".join(flags))
         if force or not os.path.exists(o) or open(o + ".stamp").read() != st if os.path.exists(o + ".stamp") else True:
-            jobs.append(([os.path.join(CUDA_HOME, "bin", "nvcc")] + NVCC_FLAGS + ["-c", p, "-o", o], o, st))
+            jobs.append(([os.path.join(CUDA_HOME, "bin", "nvcc")] + flags + ["-c", p, "-o", o], o, st))
     for src in CPP_SOURCES:
         p = os.path.join(HERE, src)
         o = os.path.join(OBJ, src + ".o")

@@ -774,6 +774,11 @@ extern "C" cudaError_t nrl_gemm_tc(const CUtensorMap* maps, const nrl::tc::TcPar
   NRL_TC_CASE(1, 128, true, true, EPI_F32)
   NRL_TC_CASE(1, 256, true, true, EPI_F32)
   NRL_TC_CASE(2, 256, true, true, EPI_F32)
+  // K-major x K-major with the float32 epilogue (hybrid decoders: projections feeding float32 recurrences / the residual)
+  NRL_TC_CASE(1, 64, false, false, EPI_F32)
+  NRL_TC_CASE(1, 128, false, false, EPI_F32)
+  NRL_TC_CASE(1, 256, false, false, EPI_F32)
+  NRL_TC_CASE(2, 256, false, false, EPI_F32)
 #undef NRL_TC_CASE
   return cudaErrorInvalidValue;
 }

@@ -1,0 +1,78 @@
+// C launch API of the kernels behind hybrid (attention + recurrent-state) decoders: stream_ops.cu, recurrent.cu,
+// attention_window.cu.  Every size is a runtime argument.  "Step plan" arrays describe one engine step of E entries
+// (each a run of consecutive tokens of one sequence) packed into T tokens:
+//   cu[E+1]        token offset of every entry        tok_entry[T]   entry of every token
+//   pos[T]         position of the token in its sequence            kv_slot[T]  physical KV slot (page * PAGE + offset)
+//   start[E]       tokens the sequence held before this step (0 = fresh state)
+//   state_slot[E]  recurrent-state slot of the entry's sequence     block_table[E, max_blocks]  KV pages
+// Storage types: `f32` flags select float (1) or bf16 (0) for a typed operand; everything that is accumulated,
+// normalised, exponentiated or carried from token to token is float.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+extern "C" {
+// x0[t] = table[tok[t]] + pos_table[pos[t]]  (float out)
+cudaError_t nrl_embed_pos(const void* embed, const void* pos_table, int w_f32, const int* tok, const int* pos, float* out,
+                          int T, int W, cudaStream_t s);
+
+// Layer boundary of a depth-weighted residual stream.  results: float [n_results_cap, stride_r] with rows of W.
+//   if (o)  results[i] = xprev + o                      (closes the previous layer)
+//   x = sum_{j <= i} dw[j] * results[j]   (dw == nullptr: x = results[i])      -> xcur (float)
+//   h = x / sqrt(mean(x^2) + eps) * g[0]                                        -> h (typed)
+cudaError_t nrl_stream_norm(float* results, long stride_r, int i, const float* o, const float* xprev, const float* dw,
+                            const float* g, float eps, float* xcur, void* h, int h_f32, int T, int W, cudaStream_t s);
+
+// out[t, c] (typed, row stride so, pre-offset) = act(in[t, c]) (float, row stride si);  act: 0 copy, 1 relu^2
+cudaError_t nrl_act_cols(const float* in, long si, void* out, long so, int out_f32, int act, int T, int C, cudaStream_t s);
+
+// Part-wise gated RMS norm:  y [T, n] float (row stride sy), gate float (row stride sg).  Parts of `part` columns.
+//   gate_first: v = y * act(gate); v /= rms_part(v); v *= w        else: v = y / rms_part(y) * w * act(gate)
+//   w index = shared_w ? (c % part) : c.   gate_act: 0 silu, 1 sigmoid.   out typed = scale * v
+cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, long sg, const float* w, int shared_w, int part,
+                                   int gate_act, int gate_first, float eps, float scale, void* out, long so, int out_f32,
+                                   int T, int n, cudaStream_t s);
+
+// Depthwise causal convolution over time with carried taps, then silu.  in float [T, C] (row stride si), w float [C, taps],
+// bias float [C] or null, state float [slots, taps-1, C] (oldest first).  out float [T, C] (row stride so).
+// nrl_causal_conv reads the old state; nrl_causal_conv_carry (launched after it) stores the step's last taps-1 inputs.
+cudaError_t nrl_causal_conv(const float* in, long si, const float* w, const float* bias, const float* state, float* out, long so,
+                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int C, int taps,
+                            cudaStream_t s);
+cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const int* cu, const int* start, const int* state_slot,
+                                  int E, int C, int taps, cudaStream_t s);
+
+// State-space scan (scalar decay per head).  xbc float [T, *] (row stride sx): x at column 0 (heads*P), B at col_b, C at col_c
+// (groups*N each).  dt_raw float (row stride sd) [T, heads].  state float [slots, heads, N, P].
+//   dt = softplus(dt_raw + dt_bias);  S = exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x      -> y float [T, heads*P]
+cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const float* dt_raw, long sd, const float* dt_bias,
+                         const float* A_log, const float* Dskip, float* state, float* y, const int* cu, const int* start,
+                         const int* state_slot, int E, int heads, int groups, int N, int P, cudaStream_t s);
+
+// Gated delta rule inputs.  qkv float [T, *] (row stride sq): q at column 0, k at col_k (kv_heads*D each); both are made unit
+// vectors per head in place (x / sqrt(sum x^2 + 1e-6)), q also times D^-1/2.  beta = sigmoid(b_raw).
+// decay = exp(-exp(A_log[h]) * softplus(a_raw + dt_bias)) with a_raw / dt_bias / decay [heads] or, per_channel, [heads*D].
+cudaError_t nrl_delta_prep(float* qkv, long sq, int col_k, const float* b_raw, long sb, const float* a_raw, long sa,
+                           const float* dt_bias, const float* A_log, float* beta, float* decay, int T, int heads, int kv_heads,
+                           int D, int per_channel, cudaStream_t s);
+
+// Gated delta rule scan.  Per head: S = g S (rows);  u = beta (v - S^T k);  S += k u^T;  o = S^T q.
+// state float [slots, heads, D, Dv];  o float [T, heads*Dv].
+cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, const float* beta, const float* decay, float* state,
+                           float* o, const int* cu, const int* start, const int* state_slot, int E, int heads, int kv_heads, int D,
+                           int Dv, int per_channel, cudaStream_t s);
+
+// Per-head RMS norm (weight [D], shared by heads) of q in place and of k into the paged cache; v into the paged cache.
+// q float [T, Hq*D] (row stride sq), k float [T, Hkv*D], v float [T, Hkv*Dv] (row strides sk, sv).
+// k_cache typed [pages, Hkv, page, D], v_cache typed [pages, Hkv, page, Dv].
+cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, const float* v, long sv, const float* qw, const float* kw,
+                                float eps, void* k_cache, void* v_cache, int cache_f32, const int* kv_slot, int T, int Hq, int Hkv,
+                                int D, int Dv, int page, cudaStream_t s);
+
+// Sliding-window softmax attention over the paged cache: token at position p sees keys p-window+1 .. p.
+// out typed (row stride so) = out_scale * softmax(scale q.k) v.
+cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
+                                 const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
+                                 float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D,
+                                 int Dv, int page, cudaStream_t s);
+}

@@ -1,0 +1,301 @@
+// Recurrent token mixers with state carried per sequence slot: short causal convolution, state-space scan with a scalar
+// decay per head, gated delta rule with a decay per head or per key channel.  One launch serves a whole engine step:
+// every entry (a run of consecutive tokens of one sequence: a prompt portion or one decoded token) starts from the state
+// its slot holds (zero when the sequence is new) and leaves the updated state there.  All arithmetic is float.
+// Compiled WITHOUT fast-math.
+#include "hybrid_kernels.h"
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// causal convolution: thread per (token, channel)
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void causal_conv_kernel(const float* __restrict__ in, long si, const float* __restrict__ w, const float* __restrict__ bias,
+                                   const float* __restrict__ state, float* __restrict__ out, long so, const int* __restrict__ cu,
+                                   const int* __restrict__ tok_entry, const int* __restrict__ start,
+                                   const int* __restrict__ state_slot, long T, int C, int taps) {
+  const long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  if (idx >= T * C) return;
+  const long t = idx / C;
+  const int c = static_cast<int>(idx - t * C);
+  const int e = tok_entry[t];
+  const long first = cu[e];
+  const int local = static_cast<int>(t - first);
+  const bool carried = start[e] > 0;
+  const float* st = state + static_cast<long>(state_slot[e]) * (taps - 1) * C;
+  float acc = bias != nullptr ? bias[c] : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int src = local - (taps - 1 - j);
+    float x = 0.f;
+    if (src >= 0) x = in[(first + src) * si + c];
+    else if (carried) x = st[static_cast<long>(taps - 1 + src) * C + c];
+    acc += w[static_cast<long>(c) * taps + j] * x;
+  }
+  out[t * so + c] = silu(acc);
+}
+
+// thread per (entry, channel): the slot keeps the last taps-1 inputs of the sequence, oldest first
+__global__ void causal_conv_carry_kernel(const float* __restrict__ in, long si, float* __restrict__ state, const int* __restrict__ cu,
+                                         const int* __restrict__ start, const int* __restrict__ state_slot, int E, int C, int taps) {
+  const long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<long>(E) * C) return;
+  const int e = static_cast<int>(idx / C);
+  const int c = static_cast<int>(idx - static_cast<long>(e) * C);
+  const long first = cu[e];
+  const int n = cu[e + 1] - cu[e];
+  const bool carried = start[e] > 0;
+  float* st = state + static_cast<long>(state_slot[e]) * (taps - 1) * C;
+  float keep[kMaxTaps];
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j) {
+    if (j < taps - 1) {
+      const int src = n - (taps - 1) + j;
+      float x = 0.f;
+      if (src >= 0) x = in[(first + src) * si + c];
+      else if (carried) x = st[static_cast<long>(taps - 1 + src) * C + c];
+      keep[j] = x;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j)
+    if (j < taps - 1) st[static_cast<long>(j) * C + c] = keep[j];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// state-space scan: block per (entry, head); thread (r, p) owns column p of S [N, P] for rows n = r, r + R, ...
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void ssd_scan_kernel(const float* __restrict__ xbc, long sx, int col_b, int col_c, const float* __restrict__ dt_raw, long sd,
+                                const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                                float* __restrict__ state, float* __restrict__ y, const int* __restrict__ cu,
+                                const int* __restrict__ start, const int* __restrict__ state_slot, int heads, int groups, int N, int P,
+                                int R) {
+  extern __shared__ float sm[];
+  float* S = sm;                         // [N][P]
+  float* vB = S + static_cast<long>(N) * P;   // [N]
+  float* vC = vB + N;                    // [N]
+  float* vx = vC + N;                    // [P]
+  float* red = vx + P;                   // [R][P]
+  const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / groups);
+  const int tid = threadIdx.x, r = tid / P, p = tid - r * P;
+  const bool live = r < R;
+  float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * N * P;
+  const bool carried = start[e] > 0;
+  for (int i = tid; i < N * P; i += blockDim.x) S[i] = carried ? gS[i] : 0.f;
+  const float negA = -expf(A_log[h]), dskip = Dskip[h], bias = dt_bias[h];
+  const int t0 = cu[e], t1 = cu[e + 1];
+  for (int t = t0; t < t1; ++t) {
+    __syncthreads();                                                     // S loaded / previous token's reads done
+    const float* row = xbc + static_cast<long>(t) * sx;
+    for (int i = tid; i < N; i += blockDim.x) {
+      vB[i] = row[col_b + g * N + i];
+      vC[i] = row[col_c + g * N + i];
+    }
+    for (int i = tid; i < P; i += blockDim.x) vx[i] = row[h * P + i];
+    const float dt = softplus(dt_raw[static_cast<long>(t) * sd + h] + bias);
+    const float a = expf(negA * dt);
+    __syncthreads();
+    float acc = 0.f;
+    if (live) {
+      const float xs = dt * vx[p];
+      for (int n = r; n < N; n += R) {
+        const float sv = a * S[n * P + p] + vB[n] * xs;
+        S[n * P + p] = sv;
+        acc += sv * vC[n];
+      }
+      red[r * P + p] = acc;
+    }
+    __syncthreads();
+    if (tid < P) {
+      float tot = 0.f;
+      for (int q = 0; q < R; ++q) tot += red[q * P + tid];
+      y[static_cast<long>(t) * heads * P + h * P + tid] = tot + dskip * vx[tid];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < N * P; i += blockDim.x) gS[i] = S[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// gated delta rule
+// ---------------------------------------------------------------------------------------------------------------------
+// block per token: warps normalise the q / k heads, then all threads form beta and the decays
+__global__ void delta_prep_kernel(float* __restrict__ qkv, long sq, int col_k, const float* __restrict__ b_raw, long sb,
+                                  const float* __restrict__ a_raw, long sa, const float* __restrict__ dt_bias,
+                                  const float* __restrict__ A_log, float* __restrict__ beta, float* __restrict__ decay, int heads,
+                                  int kv_heads, int D, int per_channel) {
+  const long t = blockIdx.x;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float qscale = 1.f / sqrtf(static_cast<float>(D));
+  for (int hh = w; hh < 2 * kv_heads; hh += nw) {
+    const bool is_k = hh >= kv_heads;
+    float* v = qkv + t * sq + (is_k ? col_k + (hh - kv_heads) * D : hh * D);
+    float ss = 0.f;
+    for (int c = lane; c < D; c += 32) ss += v[c] * v[c];
+    ss = warp_sum(ss);
+    const float r = (is_k ? 1.f : qscale) / sqrtf(ss + 1e-6f);
+    for (int c = lane; c < D; c += 32) v[c] *= r;
+  }
+  for (int hh = threadIdx.x; hh < heads; hh += blockDim.x) beta[t * heads + hh] = 1.f / (1.f + expf(-b_raw[t * sb + hh]));
+  const int nd = per_channel ? heads * D : heads;
+  for (int i = threadIdx.x; i < nd; i += blockDim.x) {
+    const int hh = per_channel ? i / D : i;
+    decay[t * nd + i] = expf(-expf(A_log[hh]) * softplus(a_raw[t * sa + i] + dt_bias[i]));
+  }
+}
+
+// block per (entry, head); thread (r, v) owns column v of S [D, Dv] for rows d = r, r + R, ...
+// One pass over S forms the decayed state, S^T k and S^T q; the read-out of the written state is o = S^T q + u (k . q).
+__global__ void delta_scan_kernel(const float* __restrict__ qkv, long sq, int col_k, int col_v, const float* __restrict__ beta,
+                                  const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o,
+                                  const int* __restrict__ cu, const int* __restrict__ start, const int* __restrict__ state_slot,
+                                  int heads, int kv_heads, int D, int Dv, int per_channel, int R) {
+  extern __shared__ float sm[];
+  float* S = sm;                              // [D][Dv]
+  float* vq = S + static_cast<long>(D) * Dv;  // [D]
+  float* vk = vq + D;                         // [D]
+  float* vg = vk + D;                         // [D]
+  float* red = vg + D;                        // [2][R][Dv]
+  float* kq = red + 2 * R * Dv;               // [1]
+  const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / kv_heads);
+  const int tid = threadIdx.x, r = tid / Dv, v = tid - r * Dv;
+  const bool live = r < R;
+  float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * D * Dv;
+  const bool carried = start[e] > 0;
+  for (int i = tid; i < D * Dv; i += blockDim.x) S[i] = carried ? gS[i] : 0.f;
+  const int t0 = cu[e], t1 = cu[e + 1];
+  const int nd = per_channel ? heads * D : heads;
+  for (int t = t0; t < t1; ++t) {
+    __syncthreads();
+    const float* row = qkv + static_cast<long>(t) * sq;
+    for (int i = tid; i < D; i += blockDim.x) {
+      vq[i] = row[g * D + i];
+      vk[i] = row[col_k + g * D + i];
+      vg[i] = per_channel ? decay[static_cast<long>(t) * nd + h * D + i] : decay[static_cast<long>(t) * nd + h];
+    }
+    __syncthreads();
+    if (tid < 32) {
+      float d = 0.f;
+      for (int i = tid; i < D; i += 32) d += vk[i] * vq[i];
+      d = warp_sum(d);
+      if (tid == 0) kq[0] = d;
+    }
+    float pk = 0.f, pq = 0.f;
+    if (live) {
+      for (int d = r; d < D; d += R) {
+        const float sv = vg[d] * S[d * Dv + v];
+        S[d * Dv + v] = sv;
+        pk += sv * vk[d];
+        pq += sv * vq[d];
+      }
+      red[r * Dv + v] = pk;
+      red[(R + r) * Dv + v] = pq;
+    }
+    __syncthreads();
+    if (live) {
+      float sk = 0.f, sq_ = 0.f;
+      for (int q = 0; q < R; ++q) {
+        sk += red[q * Dv + v];
+        sq_ += red[(R + q) * Dv + v];
+      }
+      const float u = beta[static_cast<long>(t) * heads + h] * (row[col_v + h * Dv + v] - sk);
+      if (r == 0) o[static_cast<long>(t) * heads * Dv + h * Dv + v] = sq_ + u * kq[0];
+      for (int d = r; d < D; d += R) S[d * Dv + v] += vk[d] * u;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < D * Dv; i += blockDim.x) gS[i] = S[i];
+}
+
+int pick_rows(int cols, int rows) {
+  // threads = cols * R <= 512, R <= rows
+  int R = 512 / cols;
+  if (R < 1) R = 1;
+  if (R > rows) R = rows;
+  if (R > 16) R = 16;
+  return R;
+}
+
+}  // namespace
+
+extern "C" {
+
+cudaError_t nrl_causal_conv(const float* in, long si, const float* w, const float* bias, const float* state, float* out, long so,
+                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int C, int taps,
+                            cudaStream_t s) {
+  if (T <= 0 || C <= 0) return cudaSuccess;
+  if (taps < 1 || taps > kMaxTaps) return cudaErrorInvalidValue;
+  const long n = static_cast<long>(T) * C;
+  causal_conv_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start,
+                                                                           state_slot, T, C, taps);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const int* cu, const int* start, const int* state_slot,
+                                  int E, int C, int taps, cudaStream_t s) {
+  if (E <= 0 || C <= 0 || taps <= 1) return cudaSuccess;
+  if (taps > kMaxTaps) return cudaErrorInvalidValue;
+  const long n = static_cast<long>(E) * C;
+  causal_conv_carry_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, s>>>(in, si, state, cu, start, state_slot, E, C, taps);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const float* dt_raw, long sd, const float* dt_bias,
+                         const float* A_log, const float* Dskip, float* state, float* y, const int* cu, const int* start,
+                         const int* state_slot, int E, int heads, int groups, int N, int P, cudaStream_t s) {
+  if (E <= 0) return cudaSuccess;
+  if (P > 512 || heads % groups != 0) return cudaErrorInvalidValue;
+  const int R = pick_rows(P, N);
+  const int threads = ((P * R + 31) / 32) * 32;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(N) * P + 2 * N + P + static_cast<size_t>(R) * P);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = 200 * 1024;
+  }
+  ssd_scan_kernel<<<dim3(E, heads), threads, smem, s>>>(xbc, sx, col_b, col_c, dt_raw, sd, dt_bias, A_log, Dskip, state, y, cu, start,
+                                                        state_slot, heads, groups, N, P, R);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_delta_prep(float* qkv, long sq, int col_k, const float* b_raw, long sb, const float* a_raw, long sa,
+                           const float* dt_bias, const float* A_log, float* beta, float* decay, int T, int heads, int kv_heads, int D,
+                           int per_channel, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  delta_prep_kernel<<<T, 128, 0, s>>>(qkv, sq, col_k, b_raw, sb, a_raw, sa, dt_bias, A_log, beta, decay, heads, kv_heads, D,
+                                      per_channel);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, const float* beta, const float* decay, float* state,
+                           float* o, const int* cu, const int* start, const int* state_slot, int E, int heads, int kv_heads, int D,
+                           int Dv, int per_channel, cudaStream_t s) {
+  if (E <= 0) return cudaSuccess;
+  if (Dv > 512 || heads % kv_heads != 0) return cudaErrorInvalidValue;
+  const int R = pick_rows(Dv, D);
+  const int threads = ((Dv * R + 31) / 32) * 32;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(D) * Dv + 3 * D + 2 * static_cast<size_t>(R) * Dv + 1);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = 200 * 1024;
+  }
+  delta_scan_kernel<<<dim3(E, heads), threads, smem, s>>>(qkv, sq, col_k, col_v, beta, decay, state, o, cu, start, state_slot, heads,
+                                                          kv_heads, D, Dv, per_channel, R);
+  return cudaGetLastError();
+}
+
+}  // extern "C"

@@ -19,6 +19,7 @@
 #include <algorithm>
 #include <deque>
 #include <stdexcept>
+#include <tuple>
 #include <unordered_map>
 #include <vector>
 
@@ -274,6 +275,194 @@ class Scheduler {
   std::vector<int> running_;
 };
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// StepScheduler: sequences that grow step by step (prompt portions of any size, single decoded tokens), each holding
+// KV pages (allocated when a portion reaches a new page) and ONE recurrent-state slot; pages and slots go back to
+// their free lists when a sequence is closed and are handed out again.  `plan()` turns a step (sequence, token count
+// pairs) into the packed int32 arrays the kernels read.  On top of that sits a small continuous-batching policy for
+// generation: requests wait in FIFO order, are admitted while a state slot is free and the pages of
+// prompt + max_new tokens can be set aside, and every `schedule(budget)` hands each decoding request its one token
+// first and fills the rest of the token budget with prompt portions.
+// ---------------------------------------------------------------------------------------------------------------------
+struct StepPlan {
+  // layout of `data`: tokens[T] | cu[E+1] | tok_entry[T] | pos[T] | kv_slot[T] | start[E] | state_slot[E] | block_table[E * max_blocks]
+  std::vector<int> data;
+  int E = 0, T = 0, max_blocks = 0;
+};
+
+class StepScheduler {
+ public:
+  StepScheduler(int num_blocks, int block_size, int num_slots) : bm_(num_blocks, block_size) {
+    if (num_slots <= 0) throw std::invalid_argument("num_slots must be positive");
+    for (int i = num_slots - 1; i >= 0; --i) free_slots_.push_back(i);
+  }
+
+  // ---- sequence table ----
+  int open(int reserve_tokens = 0) {
+    if (free_slots_.empty()) throw std::runtime_error("StepScheduler: no free state slot");
+    const int want = bm_.blocks_for(reserve_tokens);
+    if (want > bm_.num_free() - reserved_unused()) throw std::runtime_error("StepScheduler: not enough free KV pages to reserve");
+    StepSeq q;
+    q.slot = free_slots_.back();
+    free_slots_.pop_back();
+    q.reserved = want;
+    q.open = true;
+    int sid;
+    if (!free_ids_.empty()) { sid = free_ids_.back(); free_ids_.pop_back(); seqs_[sid] = q; }
+    else { sid = static_cast<int>(seqs_.size()); seqs_.push_back(q); }
+    return sid;
+  }
+  void close(int sid) {
+    StepSeq& q = at(sid);
+    bm_.release(q.blocks);
+    free_slots_.push_back(q.slot);
+    q = StepSeq();
+    free_ids_.push_back(sid);
+  }
+  int seq_len(int sid) const { return at(sid).len; }
+  int slot_of(int sid) const { return at(sid).slot; }
+  std::vector<int> block_table(int sid) const { return at(sid).blocks; }
+  int num_free_blocks() const { return bm_.num_free(); }
+  int num_free_slots() const { return static_cast<int>(free_slots_.size()); }
+  int num_open() const { return static_cast<int>(seqs_.size() - free_ids_.size()); }
+  int block_size() const { return bm_.block_size(); }
+
+  // Append counts[i] tokens to sids[i] (each sequence at most once per step) and describe the step.
+  StepPlan plan(const std::vector<int>& sids, const std::vector<int>& counts) {
+    if (sids.size() != counts.size()) throw std::invalid_argument("plan: sids and counts differ in length");
+    const int E = static_cast<int>(sids.size()), bs = bm_.block_size();
+    int T = 0, need = 0, unreserved_need = 0;
+    for (int i = 0; i < E; ++i) {
+      const StepSeq& q = at(sids[i]);
+      if (counts[i] <= 0) throw std::invalid_argument("plan: every entry needs at least one token");
+      for (int j = 0; j < i; ++j)
+        if (sids[j] == sids[i]) throw std::invalid_argument("plan: a sequence appears twice in one step");
+      T += counts[i];
+      const int have = static_cast<int>(q.blocks.size());
+      const int extra = std::max(0, bm_.blocks_for(q.len + counts[i]) - have);
+      need += extra;
+      unreserved_need += std::max(0, have + extra - std::max(have, q.reserved));
+    }
+    // pages set aside for other sequences stay untouched
+    if (need > bm_.num_free() || unreserved_need > bm_.num_free() - reserved_unused())
+      throw std::runtime_error("StepScheduler: out of KV pages");
+    StepPlan p;
+    p.E = E; p.T = T;
+    for (int i = 0; i < E; ++i) {
+      StepSeq& q = seqs_[sids[i]];
+      const int want = bm_.blocks_for(q.len + counts[i]);
+      const int have = static_cast<int>(q.blocks.size());
+      if (want > have) {
+        std::vector<int> more = bm_.allocate(want - have);
+        q.blocks.insert(q.blocks.end(), more.begin(), more.end());
+      }
+      p.max_blocks = std::max(p.max_blocks, static_cast<int>(q.blocks.size()));
+    }
+    const int MB = p.max_blocks;
+    p.data.assign(static_cast<size_t>(T) + (E + 1) + 3 * static_cast<size_t>(T) + 2 * E + static_cast<size_t>(E) * MB, 0);
+    int* cu = p.data.data() + T;
+    int* tok_entry = cu + E + 1;
+    int* pos = tok_entry + T;
+    int* kv_slot = pos + T;
+    int* start = kv_slot + T;
+    int* state_slot = start + E;
+    int* bt = state_slot + E;
+    int t = 0;
+    for (int i = 0; i < E; ++i) {
+      StepSeq& q = seqs_[sids[i]];
+      cu[i] = t;
+      start[i] = q.len;
+      state_slot[i] = q.slot;
+      for (int j = 0; j < counts[i]; ++j, ++t) {
+        const int ps = q.len + j;
+        tok_entry[t] = i;
+        pos[t] = ps;
+        kv_slot[t] = q.blocks[ps / bs] * bs + ps % bs;
+      }
+      std::copy(q.blocks.begin(), q.blocks.end(), bt + static_cast<size_t>(i) * MB);
+      q.len += counts[i];
+    }
+    cu[E] = t;
+    return p;
+  }
+
+  // ---- generation policy ----
+  int submit(int prompt_len, int max_new) {
+    if (prompt_len <= 0 || max_new <= 0) throw std::invalid_argument("bad request");
+    if (bm_.blocks_for(prompt_len + max_new) > bm_.num_blocks()) throw std::runtime_error("request can never fit in the KV pool");
+    Req r;
+    r.prompt_len = prompt_len; r.max_new = max_new; r.total = prompt_len;
+    reqs_.push_back(r);
+    waiting_.push_back(static_cast<int>(reqs_.size()) - 1);
+    return static_cast<int>(reqs_.size()) - 1;
+  }
+  // -> (request ids, first token index within the request, token counts); the caller runs plan() on seq_of(rid)
+  std::tuple<std::vector<int>, std::vector<int>, std::vector<int>> schedule(int budget) {
+    while (!waiting_.empty() && !free_slots_.empty()) {
+      Req& r = reqs_[waiting_.front()];
+      if (bm_.blocks_for(r.prompt_len + r.max_new) > bm_.num_free() - reserved_unused()) break;
+      r.sid = open(r.prompt_len + r.max_new);
+      running_.push_back(waiting_.front());
+      waiting_.pop_front();
+    }
+    std::vector<int> ids, offs, cnts;
+    for (int pass = 0; pass < 2; ++pass)                     // decoding requests first, then prompt portions
+      for (int rid : running_) {
+        const Req& r = reqs_[rid];
+        const int pending = r.total - r.fed;
+        const bool decoding = r.fed >= r.prompt_len;
+        if (pending <= 0 || decoding != (pass == 0) || budget <= 0) continue;
+        const int n = std::min(pending, budget);
+        ids.push_back(rid); offs.push_back(r.fed); cnts.push_back(n);
+        budget -= n;
+      }
+    return {ids, offs, cnts};
+  }
+  void fed(int rid, int n) { reqs_.at(rid).fed += n; }
+  void push_token(int rid) { ++reqs_.at(rid).total; }
+  void finish(int rid) {
+    Req& r = reqs_.at(rid);
+    if (r.sid < 0) return;
+    close(r.sid);
+    r.sid = -1;
+    running_.erase(std::remove(running_.begin(), running_.end(), rid), running_.end());
+  }
+  int seq_of(int rid) const { return reqs_.at(rid).sid; }
+  int num_waiting() const { return static_cast<int>(waiting_.size()); }
+  int num_running() const { return static_cast<int>(running_.size()); }
+
+ private:
+  struct StepSeq {
+    int slot = -1, len = 0, reserved = 0;
+    bool open = false;
+    std::vector<int> blocks;
+  };
+  struct Req {
+    int prompt_len = 0, max_new = 0, total = 0, fed = 0, sid = -1;
+  };
+  StepSeq& at(int sid) {
+    if (sid < 0 || sid >= static_cast<int>(seqs_.size()) || !seqs_[sid].open) throw std::invalid_argument("unknown sequence");
+    return seqs_[sid];
+  }
+  const StepSeq& at(int sid) const { return const_cast<StepScheduler*>(this)->at(sid); }
+
+  // pages set aside at open() and not allocated yet
+  int reserved_unused() const {
+    int n = 0;
+    for (const StepSeq& q : seqs_)
+      if (q.open) n += std::max(0, q.reserved - static_cast<int>(q.blocks.size()));
+    return n;
+  }
+
+  BlockManager bm_;
+  std::vector<int> free_slots_, free_ids_;
+  std::vector<StepSeq> seqs_;
+  std::vector<Req> reqs_;
+  std::deque<int> waiting_;
+  std::vector<int> running_;
+};
+
 #ifndef NRL_RUNTIME_NO_PYBIND
 void bind_runtime(py::module_& m) {
   py::class_<BlockManager>(m, "BlockManager")
@@ -309,6 +498,31 @@ void bind_runtime(py::module_& m) {
       .def("is_finished", &Scheduler::is_finished)
       .def("running_groups", &Scheduler::running_groups)
       .def("prefill_slots", &Scheduler::prefill_slots);
+  py::class_<StepScheduler>(m, "StepScheduler")
+      .def(py::init<int, int, int>(), py::arg("num_blocks"), py::arg("block_size"), py::arg("num_slots"))
+      .def("open", &StepScheduler::open, py::arg("reserve_tokens") = 0)
+      .def("close", &StepScheduler::close)
+      .def("seq_len", &StepScheduler::seq_len)
+      .def("slot_of", &StepScheduler::slot_of)
+      .def("block_table", &StepScheduler::block_table)
+      .def("num_free_blocks", &StepScheduler::num_free_blocks)
+      .def("num_free_slots", &StepScheduler::num_free_slots)
+      .def("num_open", &StepScheduler::num_open)
+      .def("block_size", &StepScheduler::block_size)
+      .def("plan", [](StepScheduler& self, const std::vector<int>& sids, const std::vector<int>& counts) {
+             StepPlan p = self.plan(sids, counts);
+             py::array_t<int> out(static_cast<py::ssize_t>(p.data.size()));
+             std::copy(p.data.begin(), p.data.end(), out.mutable_data());
+             return py::make_tuple(out, p.E, p.T, p.max_blocks);
+           }, py::arg("seq_ids"), py::arg("counts"))
+      .def("submit", &StepScheduler::submit)
+      .def("schedule", &StepScheduler::schedule)
+      .def("fed", &StepScheduler::fed)
+      .def("push_token", &StepScheduler::push_token)
+      .def("finish", &StepScheduler::finish)
+      .def("seq_of", &StepScheduler::seq_of)
+      .def("num_waiting", &StepScheduler::num_waiting)
+      .def("num_running", &StepScheduler::num_running);
 }
 #endif
 

@@ -1,0 +1,177 @@
+// Residual-stream and normalisation kernels of hybrid decoders (float stream, typed GEMM operands):
+// learned-position embedding, depth-weighted stream + single-gain RMS norm, part-wise gated RMS norm, column activations.
+// Compiled WITHOUT fast-math: the float32 serving mode must stay within float rounding of a plain evaluation.
+#include <cuda_bf16.h>
+
+#include "hybrid_kernels.h"
+
+namespace {
+
+__device__ __forceinline__ float ld(const float* p, long i) { return p[i]; }
+__device__ __forceinline__ float ld(const __nv_bfloat16* p, long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st(float* p, long i, float v) { p[i] = v; }
+__device__ __forceinline__ void st(__nv_bfloat16* p, long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// sum over the block; every thread gets the result.  red: >= 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+template <typename WT>
+__global__ void embed_pos_kernel(const WT* __restrict__ embed, const WT* __restrict__ ptab, const int* __restrict__ tok,
+                                 const int* __restrict__ pos, float* __restrict__ out, int W) {
+  const long t = blockIdx.x;
+  const long a = static_cast<long>(tok[t]) * W, b = static_cast<long>(pos[t]) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) out[t * W + c] = ld(embed, a + c) + ld(ptab, b + c);
+}
+
+template <typename HT>
+__global__ void stream_norm_kernel(float* __restrict__ results, long stride_r, int i, const float* __restrict__ o,
+                                   const float* __restrict__ xprev, const float* __restrict__ dw, const float* __restrict__ g,
+                                   float eps, float* __restrict__ xcur, HT* __restrict__ h, int W) {
+  __shared__ float red[32];
+  const long row = static_cast<long>(blockIdx.x) * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float last;
+    if (o != nullptr) {
+      last = xprev[row + c] + o[row + c];
+      results[i * stride_r + row + c] = last;
+    } else {
+      last = results[i * stride_r + row + c];
+    }
+    float x;
+    if (dw != nullptr) {
+      x = 0.f;
+      for (int j = 0; j < i; ++j) x += dw[j] * results[j * stride_r + row + c];
+      x += dw[i] * last;
+    } else {
+      x = last;
+    }
+    xcur[row + c] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  const float r = g[0] / sqrtf(ss / static_cast<float>(W) + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) st(h, row + c, xcur[row + c] * r);
+}
+
+template <typename OT>
+__global__ void act_cols_kernel(const float* __restrict__ in, long si, OT* __restrict__ out, long so, int act, long T, int C) {
+  const long n = T * C;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = idx / C;
+    const int c = static_cast<int>(idx - t * C);
+    float v = in[t * si + c];
+    if (act == 1) {
+      v = fmaxf(v, 0.f);
+      v = v * v;
+    }
+    st(out, t * so + c, v);
+  }
+}
+
+__device__ __forceinline__ float gate_fn(float z, int act) {
+  const float sg = 1.f / (1.f + expf(-z));
+  return act == 0 ? z * sg : sg;
+}
+
+// one warp per (token, part)
+template <typename OT>
+__global__ void gated_part_rmsnorm_kernel(const float* __restrict__ y, long sy, const float* __restrict__ gate, long sg,
+                                          const float* __restrict__ w, int shared_w, int part, int gate_act, int gate_first,
+                                          float eps, float scale, OT* __restrict__ out, long so, long T, int nparts) {
+  const long wid = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= T * nparts) return;
+  const long t = wid / nparts;
+  const int p = static_cast<int>(wid - t * nparts);
+  const float* yr = y + t * sy + static_cast<long>(p) * part;
+  const float* gr = gate + t * sg + static_cast<long>(p) * part;
+  float ss = 0.f;
+  for (int c = lane; c < part; c += 32) {
+    float v = yr[c];
+    if (gate_first) v *= gate_fn(gr[c], gate_act);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / static_cast<float>(part) + eps);
+  for (int c = lane; c < part; c += 32) {
+    float v = yr[c];
+    const float gv = gate_fn(gr[c], gate_act);
+    const float wv = w[shared_w ? c : p * part + c];
+    v = gate_first ? (v * gv) * r * wv : v * r * wv * gv;
+    st(out, t * so + static_cast<long>(p) * part + c, scale * v);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+cudaError_t nrl_embed_pos(const void* embed, const void* pos_table, int w_f32, const int* tok, const int* pos, float* out, int T,
+                          int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  const int th = W >= 256 ? 256 : 128;
+  if (w_f32)
+    embed_pos_kernel<float><<<T, th, 0, s>>>(static_cast<const float*>(embed), static_cast<const float*>(pos_table), tok, pos, out, W);
+  else
+    embed_pos_kernel<__nv_bfloat16><<<T, th, 0, s>>>(static_cast<const __nv_bfloat16*>(embed),
+                                                    static_cast<const __nv_bfloat16*>(pos_table), tok, pos, out, W);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_stream_norm(float* results, long stride_r, int i, const float* o, const float* xprev, const float* dw,
+                            const float* g, float eps, float* xcur, void* h, int h_f32, int T, int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  const int th = W >= 1024 ? 256 : 128;
+  if (h_f32)
+    stream_norm_kernel<float><<<T, th, 0, s>>>(results, stride_r, i, o, xprev, dw, g, eps, xcur, static_cast<float*>(h), W);
+  else
+    stream_norm_kernel<__nv_bfloat16><<<T, th, 0, s>>>(results, stride_r, i, o, xprev, dw, g, eps, xcur,
+                                                      static_cast<__nv_bfloat16*>(h), W);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_act_cols(const float* in, long si, void* out, long so, int out_f32, int act, int T, int C, cudaStream_t s) {
+  if (T <= 0 || C <= 0) return cudaSuccess;
+  const long n = static_cast<long>(T) * C;
+  const int blocks = static_cast<int>((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (out_f32)
+    act_cols_kernel<float><<<blocks, 256, 0, s>>>(in, si, static_cast<float*>(out), so, act, T, C);
+  else
+    act_cols_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(in, si, static_cast<__nv_bfloat16*>(out), so, act, T, C);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, long sg, const float* w, int shared_w, int part,
+                                   int gate_act, int gate_first, float eps, float scale, void* out, long so, int out_f32, int T,
+                                   int n, cudaStream_t s) {
+  if (T <= 0 || n <= 0) return cudaSuccess;
+  if (part <= 0 || n % part != 0) return cudaErrorInvalidValue;
+  const int nparts = n / part;
+  const long warps = static_cast<long>(T) * nparts;
+  const int blocks = static_cast<int>((warps + 3) / 4);
+  if (out_f32)
+    gated_part_rmsnorm_kernel<float><<<blocks, 128, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale,
+                                                            static_cast<float*>(out), so, T, nparts);
+  else
+    gated_part_rmsnorm_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps,
+                                                                    scale, static_cast<__nv_bfloat16*>(out), so, T, nparts);
+  return cudaGetLastError();
+}
+
+}  // extern "C"

@@ -25,6 +25,7 @@ import torch.nn as nn
 import torch.utils.checkpoint
 
 from .. import ops
+from .registry import register_model
 
 
 @dataclass
@@ -280,6 +281,7 @@ class Qwen2PreTrained(nn.Module):
         return model
 
 
+@register_model("Qwen2ForCausalLM", "qwen2", sampler="native")
 class Qwen2ForCausalLM(Qwen2PreTrained):
     def __init__(self, cfg: Qwen2Config):
         super().__init__(cfg)

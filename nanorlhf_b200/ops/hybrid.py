@@ -1,0 +1,66 @@
+"""Op layer of hybrid (attention + recurrent-state) decoders: thin, launch-counting wrappers over the sm_100a kernels of
+``csrc/stream_ops.cu``, ``csrc/recurrent.cu`` and ``csrc/attention_window.cu``.
+
+All of them take the step plan of ``_C.StepScheduler.plan`` (entries = runs of consecutive tokens of one sequence) and
+work on packed ``[tokens, ...]`` tensors; recurrent state and convolution taps live in per-sequence slots, keys and values
+in 16-token pages.  There is no PyTorch fallback: these ops exist on CUDA only.
+"""
+from __future__ import annotations
+
+from . import native
+
+
+def _ext():
+    return native.ext()
+
+
+def embed_pos(embed, pos_table, tok, pos, out):
+    native._count()
+    _ext().embed_pos(embed, pos_table, tok, pos, out)
+    return out
+
+
+def stream_norm(results, i, o, xprev, dw, gain, eps, xcur, h, T):
+    """Close layer ``i - 1`` (``results[i] = xprev + o``), form ``x = sum_j dw[j] results[j]`` and ``h = rmsnorm(x) * gain``."""
+    native._count()
+    _ext().stream_norm(results, i, o, xprev, dw, gain, eps, xcur, h, T)
+
+
+def act_cols(x, out, act: str = "copy"):
+    native._count()
+    _ext().act_cols(x, out, {"copy": 0, "relu2": 1}[act])
+
+
+def gated_part_rmsnorm(y, gate, w, part, gate_act, gate_first, eps, scale, out):
+    native._count()
+    _ext().gated_part_rmsnorm(y, gate, w, part, {"silu": 0, "sigmoid": 1}[gate_act], gate_first, eps, scale, out)
+
+
+def causal_conv(x, w, bias, state, out, plan):
+    native._count(2)
+    _ext().causal_conv(x, w, bias, state, out, plan.cu, plan.tok_entry, plan.start, plan.state_slot)
+
+
+def ssd_scan(xbc, col_b, col_c, dt_raw, dt_bias, A_log, D, state, y, plan, groups):
+    native._count()
+    _ext().ssd_scan(xbc, col_b, col_c, dt_raw, dt_bias, A_log, D, state, y, plan.cu, plan.start, plan.state_slot, groups)
+
+
+def delta_prep(qkv, col_k, b_raw, a_raw, dt_bias, A_log, beta, decay, kv_heads, dim, per_channel):
+    native._count()
+    _ext().delta_prep(qkv, col_k, b_raw, a_raw, dt_bias, A_log, beta, decay, kv_heads, dim, per_channel)
+
+
+def delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan, kv_heads, per_channel):
+    native._count()
+    _ext().delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan.cu, plan.start, plan.state_slot, kv_heads, per_channel)
+
+
+def qknorm_kv_write(q, k, v, qw, kw, eps, k_cache, v_cache, plan):
+    native._count()
+    _ext().qknorm_kv_write(q, k, v, qw, kw, eps, k_cache, v_cache, plan.kv_slot)
+
+
+def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out):
+    native._count()
+    _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out)

@@ -57,7 +57,11 @@ def get_native_engine(model, **kw):
     """One persistent native engine per policy object (no boot/teardown per rollout).  The engine hangs off the
     policy module itself, so its weight arena and KV pages are released with the model (no process-global cache);
     ``release_native_engine`` frees them earlier."""
-    from .native_sampler import NativeSampler
+    from ..models.registry import sampler_kind
+    if sampler_kind(model) == "hybrid":          # attention + recurrent-state decoders run on the step engine
+        from .hybrid_sampler import HybridSampler as NativeSampler
+    else:
+        from .native_sampler import NativeSampler
     pol = getattr(model, "policy", model)
     eng = pol.__dict__.get("_nrl_sampler")
     comm = kw.pop("weight_sync_comm", None)

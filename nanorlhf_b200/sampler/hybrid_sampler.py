@@ -1,0 +1,406 @@
+"""Step engine for hybrid decoders: layers that mix paged-KV attention with recurrent state (state-space scans, delta rules).
+
+Where ``NativeSampler`` prefills whole prompts and then decodes one token per row, this engine runs STEPS: a step is a
+batch of entries, each a run of consecutive tokens of one sequence -- a prompt portion of any length or a single decoded
+token -- executed together by the same kernels.  That is what recurrent layers need (their state is carried from step to
+step in a per-sequence slot) and it gives chunked prefill and continuous batching for free:
+
+* sequences, KV pages (16 tokens) and state slots are owned by the C++ ``StepScheduler`` (csrc/runtime.cpp), which also
+  builds each step's packed plan (token offsets, positions, KV slots, block tables, state slots) and runs the admission /
+  token-budget policy of ``generate``;
+* per layer the weights are fused into TWO matrices: every projection that reads the normed stream (q, k, v, state-space
+  input, gates, decays, feed-forward up) is one GEMM, and every projection that writes the stream (attention out,
+  state-space out, feed-forward down) is one GEMM over the concatenated activations, mixer scales folded into the
+  activations;
+* the residual stream, its depth-weighted average, norms, scores, softmax, decays and recurrent state are float32 in both
+  serving modes; ``dtype="bf16"`` keeps GEMM operands and KV pages in bf16 (fp32 accumulation, fp32 GEMM results),
+  ``dtype="fp32"`` keeps everything in float32 with TF32 off;
+* ``generate`` has the call shape and sampling semantics of ``NativeSampler.generate`` (temperature, top-p, n samples per
+  prompt, seeded per-row streams, EOS kept, right-padded).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..ops import gemm as _gemm, hybrid as hy, native
+
+
+def _unwrap(model):
+    m = getattr(model, "policy", model)
+    return getattr(m, "base_model", m) if hasattr(m, "peft_config") else m
+
+
+class StepPlan:
+    """Device views of one step's packed plan (layout fixed by ``StepScheduler.plan``)."""
+    __slots__ = ("E", "T", "max_blocks", "tokens", "cu", "tok_entry", "pos", "kv_slot", "start", "state_slot", "block_table")
+
+    def __init__(self, buf: torch.Tensor, E: int, T: int, MB: int):
+        self.E, self.T, self.max_blocks = E, T, MB
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = buf[o:o + n]
+            o += n
+            return v
+        self.tokens, self.cu, self.tok_entry, self.pos, self.kv_slot = take(T), take(E + 1), take(T), take(T), take(T)
+        self.start, self.state_slot = take(E), take(E)
+        self.block_table = take(E * MB).view(E, MB)
+
+
+class _Mixer:
+    __slots__ = ("spec", "cols", "out_col", "out_size", "vec", "k_cache", "v_cache", "conv_state", "state", "w_lr2", "lr_cols", "rank")
+
+
+class _Layer:
+    __slots__ = ("spec", "gain", "dw", "w_in", "w_out", "mixers", "ff_col", "ff_out_col", "n_in", "k_out", "out_pad")
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+class HybridSampler:
+    PAGE = 16
+
+    def __init__(self, model, dtype: str = "bf16", kv_block_size: int = 16, max_num_seqs: int = 64, pool_tokens: Optional[int] = None,
+                 prefill_token_budget: int = 8192, gemm: str = "tc", rollout_dtype: Optional[str] = None, **_unused):
+        if kv_block_size != self.PAGE:
+            raise ValueError("KV pages hold 16 tokens")
+        native.load()
+        dtype = {"bfloat16": "bf16", "float32": "fp32"}.get(rollout_dtype or dtype, rollout_dtype or dtype)
+        if dtype not in ("bf16", "fp32"):
+            raise ValueError(f"unknown serving dtype {dtype!r}")
+        self.model = model
+        self.lm = _unwrap(model)
+        self.cfg = self.lm.config
+        self.device = next(self.lm.parameters()).device
+        if self.device.type != "cuda":
+            raise RuntimeError("the step engine runs on CUDA only")
+        self.rollout_dtype = dtype
+        self.fp32 = dtype == "fp32"
+        self.wdtype = torch.float32 if self.fp32 else torch.bfloat16
+        if self.fp32:                                     # true float32 products
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+        self.gemm_backend = gemm
+        self.max_num_seqs = max_num_seqs
+        self.pool_tokens = pool_tokens
+        self.prefill_token_budget = prefill_token_budget
+        self.sharded_sync = None
+        self._weights_version = None
+        self.layers: List[_Layer] = []
+        self.sched = None
+        self.num_blocks = 0
+        self.stats = {"steps": 0, "tokens": 0, "decode_tokens": 0, "prefill_tokens": 0}
+        self._build_arena()
+
+    # ------------------------------------------------------------------------------------------
+    # weights: two fused matrices per layer + float vectors
+    # ------------------------------------------------------------------------------------------
+    def _t(self, name):
+        return self.lm.tensor(name).detach()
+
+    def _f(self, name):
+        return self._t(name).to(device=self.device, dtype=torch.float32).contiguous()
+
+    @torch.no_grad()
+    def _build_arena(self):
+        lm, dev, wd = self.lm, self.device, self.wdtype
+        W = self.cfg.width
+        self.layers = []
+        for spec in lm.layer_specs():
+            p = f"l{spec.index}."
+            L = _Layer()
+            L.spec = spec
+            L.gain = self._f(p + "norm1").reshape(1)
+            L.dw = self._f(p + "dwa")
+            rows_in: List[torch.Tensor] = []
+            cols_out: List[torch.Tensor] = []
+            n_in = k_out = 0
+            L.mixers = []
+
+            def add_in(name):
+                nonlocal n_in
+                t = self._t(name)
+                rows_in.append(t)
+                c = (n_in, t.shape[0])
+                n_in += t.shape[0]
+                return c
+
+            def add_out(name):
+                nonlocal k_out
+                t = self._t(name)
+                cols_out.append(t)
+                c = k_out
+                k_out += t.shape[1]
+                return c, t.shape[1]
+
+            for ms in spec.mixers:
+                M = _Mixer()
+                M.spec, M.cols, M.vec = ms, {}, {}
+                M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = None
+                q = ms.prefix
+                if ms.kind == "window_attention":
+                    for n in ("q", "k", "v"):
+                        M.cols[n] = add_in(q + n)
+                    M.vec["qw"], M.vec["kw"] = self._f(q + "q.norm"), self._f(q + "k.norm")
+                elif ms.kind == "ssd":
+                    M.cols["in"] = add_in(q + "in")
+                    for n in ("conv", "conv.b", "dt_bias", "A_log", "D", "norm"):
+                        M.vec[n] = self._f(q + n)
+                elif ms.kind == "gated_delta":
+                    for n in ("q", "k", "v", "b"):
+                        M.cols[n] = add_in(q + n)
+                    if ms.per_channel:
+                        M.cols["a1"], M.cols["g1"] = add_in(q + "a1"), add_in(q + "g1")
+                        a2, g2 = self._t(q + "a2"), self._t(q + "g2")
+                        r = a2.shape[1]
+                        M.rank = r
+                        na, ng = a2.shape[0], g2.shape[0]
+                        w2 = torch.zeros(_pad8(na + ng), _pad8(2 * r), dtype=wd, device=dev)     # block diagonal: [a2 0; 0 g2]
+                        w2[:na, :r] = a2.to(wd)
+                        w2[na:na + ng, r:2 * r] = g2.to(wd)
+                        M.w_lr2, M.lr_cols = w2, (na, ng)
+                    else:
+                        M.cols["a"], M.cols["g"] = add_in(q + "a"), add_in(q + "g")
+                    M.vec["conv"] = torch.cat([self._f(q + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
+                    for n in ("dt_bias", "A_log", "norm"):
+                        M.vec[n] = self._f(q + n)
+                else:
+                    raise ValueError(f"unknown mixer kind {ms.kind!r}")
+                M.out_col, M.out_size = add_out(q + "o")
+                L.mixers.append(M)
+            L.ff_col = L.ff_out_col = None
+            if spec.ff:
+                L.ff_col = add_in(p + "mlp.up")
+                L.ff_out_col = add_out(p + "mlp.down")
+            L.n_in, L.k_out = _pad8(n_in), _pad8(k_out)
+            L.out_pad = L.k_out != k_out
+            L.w_in = torch.zeros(L.n_in, W, dtype=wd, device=dev)
+            L.w_in[:n_in] = torch.cat([t.to(device=dev, dtype=wd) for t in rows_in], 0)
+            L.w_out = torch.zeros(W, L.k_out, dtype=wd, device=dev)
+            L.w_out[:, :k_out] = torch.cat([t.to(device=dev, dtype=wd) for t in cols_out], 1)
+            self.layers.append(L)
+        self.embed = self._t("embed").to(device=dev, dtype=wd).contiguous()
+        self.pos_table = self._t("pos").to(device=dev, dtype=wd).contiguous()
+        self.final_gain = self._f("final.norm").reshape(1)
+        V = self.cfg.vocab
+        self.head = torch.zeros(_pad8(V), W, dtype=wd, device=dev)
+        self.head[:V] = self._t("head").to(device=dev, dtype=wd)
+        self._weights_version = self.weights_fingerprint()
+
+    def weights_fingerprint(self):
+        return getattr(self.lm, "_nrl_version", 0)
+
+    def sync_weights(self, force: bool = False):
+        """Re-fuse the arena when the model's weights changed (the optimizer bumps ``_nrl_version``)."""
+        if force or self._weights_version != self.weights_fingerprint():
+            pools = [(M.k_cache, M.v_cache, M.conv_state, M.state) for L in self.layers for M in L.mixers]
+            self._build_arena()
+            for M, pl in zip([M for L in self.layers for M in L.mixers], pools):
+                M.k_cache, M.v_cache, M.conv_state, M.state = pl
+
+    def release(self):
+        self.layers, self.sched, self.num_blocks = [], None, 0
+
+    # ------------------------------------------------------------------------------------------
+    # cache pages and state slots
+    # ------------------------------------------------------------------------------------------
+    def reset_pool(self, pool_tokens: int, num_slots: int):
+        """(Re)build the page pool for ``pool_tokens`` tokens and ``num_slots`` state slots; all sequences are dropped."""
+        from .. import _C
+        dev, wd = self.device, self.wdtype
+        n = max(1, (pool_tokens + self.PAGE - 1) // self.PAGE)
+        f32 = dict(dtype=torch.float32, device=dev)
+        for L in self.layers:
+            for M in L.mixers:
+                ms = M.spec
+                if ms.kind == "window_attention":
+                    M.k_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.dim, dtype=wd, device=dev)
+                    M.v_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.vdim, dtype=wd, device=dev)
+                elif ms.kind == "ssd":
+                    ch = ms.heads * ms.vdim + 2 * ms.kv_heads * ms.dim
+                    M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
+                    M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
+                else:
+                    ch = 2 * ms.kv_heads * ms.dim + ms.heads * ms.vdim
+                    M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
+                    M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
+        self.num_blocks, self.num_slots = n, num_slots
+        self.sched = _C.StepScheduler(n, self.PAGE, num_slots)
+
+    def open(self, reserve_tokens: int = 0) -> int:
+        """Admit a sequence: it gets a state slot now and KV pages as its tokens arrive."""
+        return self.sched.open(reserve_tokens)
+
+    def close(self, sid: int):
+        """Give the sequence's pages and state slot back."""
+        self.sched.close(sid)
+
+    # ------------------------------------------------------------------------------------------
+    # the step
+    # ------------------------------------------------------------------------------------------
+    def _mm(self, x, w):
+        """x [T, K] . w [N, K]^T -> float32 [T, N]."""
+        if self.fp32:
+            return torch.mm(x, w.t())
+        if (self.gemm_backend == "tc" and x.shape[1] % 64 == 0 and w.shape[0] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+                and x.data_ptr() % 16 == 0):
+            out = torch.empty(x.shape[0], w.shape[0], dtype=torch.float32, device=x.device)
+            _gemm.gemm(x, w, out_f32=out)                 # tcgen05 GEMM with the float32 epilogue (csrc/gemm_tc.cu)
+            return out
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]]) -> torch.Tensor:
+        """Run one batch.  ``entries``: (sequence id, its next tokens, indices among them whose logits are wanted).
+        Returns float32 logits [wanted, vocab] in entry order."""
+        sids = [int(e[0]) for e in entries]
+        counts = [len(e[1]) for e in entries]
+        data, E, T, MB = self.sched.plan(sids, counts)
+        o, rows = 0, []
+        for (_sid, toks, want), c in zip(entries, counts):
+            data[o:o + c] = np.asarray(toks, dtype=np.int32)
+            rows += [o + int(j) for j in want]
+            o += c
+        plan = StepPlan(torch.from_numpy(data).to(self.device), E, T, MB)
+        self.stats["steps"] += 1
+        self.stats["tokens"] += T
+        return self._forward(plan, rows)
+
+    def _forward(self, plan: StepPlan, rows: List[int]) -> torch.Tensor:
+        cfg, dev, wd = self.cfg, self.device, self.wdtype
+        T, W, eps = plan.T, cfg.width, cfg.norm_eps
+        f32 = dict(dtype=torch.float32, device=dev)
+        nl = len(self.layers)
+        results = torch.empty(nl + 1, T, W, **f32)
+        hy.embed_pos(self.embed, self.pos_table, plan.tokens, plan.pos, results[0])
+        xbuf = [torch.empty(T, W, **f32), torch.empty(T, W, **f32)]
+        h = torch.empty(T, W, dtype=wd, device=dev)
+        o = xprev = None
+        for i, L in enumerate(self.layers):
+            xcur = xbuf[i & 1]
+            hy.stream_norm(results, i, o, xprev, self.layers[i - 1].dw if i else None, L.gain, eps, xcur, h, T)
+            U = self._mm(h, L.w_in)                                                   # [T, n_in] float
+            A = (torch.zeros if L.out_pad else torch.empty)(T, L.k_out, dtype=wd, device=dev)
+            for M in L.mixers:
+                out = A[:, M.out_col:M.out_col + M.out_size]
+                if M.spec.kind == "window_attention":
+                    self._window_attention(M, U, plan, eps, out)
+                elif M.spec.kind == "ssd":
+                    self._ssd(M, U, plan, eps, out)
+                else:
+                    self._gated_delta(M, U, plan, eps, out)
+            if L.ff_col is not None:
+                c, n = L.ff_col
+                oc, on = L.ff_out_col
+                hy.act_cols(U[:, c:c + n], A[:, oc:oc + on], "relu2")
+            o = self._mm(A, L.w_out)                                                  # [T, W] float
+            xprev = xcur
+        hy.stream_norm(results, nl, o, xprev, self.layers[-1].dw, self.final_gain, eps, xbuf[nl & 1], h, T)
+        if not rows:
+            return torch.empty(0, cfg.vocab, **f32)
+        hw = h if rows == list(range(T)) else h[torch.tensor(rows, device=dev)]
+        return self._mm(hw.contiguous(), self.head)[:, :cfg.vocab]
+
+    def _window_attention(self, M, U, plan, eps, out):
+        ms = M.spec
+        (cq, nq), (ck, nk), (cv, nv) = M.cols["q"], M.cols["k"], M.cols["v"]
+        q = U[:, cq:cq + nq]
+        hy.qknorm_kv_write(q, U[:, ck:ck + nk], U[:, cv:cv + nv], M.vec["qw"], M.vec["kw"], eps, M.k_cache, M.v_cache, plan)
+        hy.window_attention(q, M.k_cache, M.v_cache, plan, ms.window, ms.scale, ms.out_scale, out)
+
+    def _ssd(self, M, U, plan, eps, out):
+        ms = M.spec
+        T = plan.T
+        inner, gn = ms.heads * ms.vdim, ms.kv_heads * ms.dim
+        ch = inner + 2 * gn
+        c0, _ = M.cols["in"]
+        z, raw, dt_raw = U[:, c0:c0 + inner], U[:, c0 + inner:c0 + inner + ch], U[:, c0 + inner + ch:c0 + inner + ch + ms.heads]
+        xbc = torch.empty(T, ch, dtype=torch.float32, device=U.device)
+        hy.causal_conv(raw, M.vec["conv"], M.vec["conv.b"], M.conv_state, xbc, plan)
+        y = torch.empty(T, inner, dtype=torch.float32, device=U.device)
+        hy.ssd_scan(xbc, inner, inner + gn, dt_raw, M.vec["dt_bias"], M.vec["A_log"], M.vec["D"], M.state, y, plan, ms.kv_heads)
+        hy.gated_part_rmsnorm(y, z, M.vec["norm"], inner // ms.norm_groups, "silu", True, eps, ms.out_scale, out)
+
+    def _gated_delta(self, M, U, plan, eps, out):
+        ms = M.spec
+        T, dev = plan.T, U.device
+        nk, nv = ms.kv_heads * ms.dim, ms.heads * ms.vdim
+        cq, _ = M.cols["q"]
+        qkv = torch.empty(T, 2 * nk + nv, dtype=torch.float32, device=dev)
+        hy.causal_conv(U[:, cq:cq + 2 * nk + nv], M.vec["conv"], None, M.conv_state, qkv, plan)
+        cb, nb = M.cols["b"]
+        if ms.per_channel:
+            c1, r = M.cols["a1"]
+            t1 = (torch.zeros if M.w_lr2.shape[1] != 2 * r else torch.empty)(T, M.w_lr2.shape[1], dtype=self.wdtype, device=dev)
+            hy.act_cols(U[:, c1:c1 + 2 * r], t1[:, :2 * r], "copy")
+            ag = self._mm(t1, M.w_lr2)
+            na, ng = M.lr_cols
+            a_raw, gate = ag[:, :na], ag[:, na:na + ng]
+        else:
+            (ca, na), (cg, ng) = M.cols["a"], M.cols["g"]
+            a_raw, gate = U[:, ca:ca + na], U[:, cg:cg + ng]
+        beta = torch.empty(T, ms.heads, dtype=torch.float32, device=dev)
+        decay = torch.empty(T, na, dtype=torch.float32, device=dev)
+        hy.delta_prep(qkv, nk, U[:, cb:cb + nb], a_raw, M.vec["dt_bias"], M.vec["A_log"], beta, decay, ms.kv_heads, ms.dim, ms.per_channel)
+        o = torch.empty(T, nv, dtype=torch.float32, device=dev)
+        hy.delta_scan(qkv, nk, 2 * nk, beta, decay, M.state, o, plan, ms.kv_heads, ms.per_channel)
+        hy.gated_part_rmsnorm(o, gate, M.vec["norm"], ms.vdim, "sigmoid" if ms.per_channel else "silu", False, eps, ms.out_scale, out)
+
+    # ------------------------------------------------------------------------------------------
+    # generation: continuous batching with chunked prefill on top of step()
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], n: int, temperature: float, top_p: float, max_tokens: int,
+                 eos_id: Optional[int], pad_id: int, seed: int) -> torch.Tensor:
+        dev = self.device
+        total = len(prompts) * n
+        out = torch.full((total, max_tokens), pad_id, dtype=torch.long)
+        if any(len(p) + max_tokens > self.cfg.max_positions for p in prompts):
+            raise ValueError("prompt + max_tokens exceeds the model's learned positions")
+        slots = min(total, self.max_num_seqs)
+        per_seq = [(len(p) + max_tokens + self.PAGE - 1) // self.PAGE * self.PAGE for p in prompts for _ in range(n)]
+        need = self.pool_tokens or sum(sorted(per_seq, reverse=True)[:slots])
+        if self.sched is None or self.sched.num_open() or self.num_blocks * self.PAGE < need or self.num_slots < slots:
+            self.reset_pool(need, slots)
+        sched = self.sched
+        toks: Dict[int, List[int]] = {}
+        gen: Dict[int, int] = {}
+        for p in prompts:
+            for _ in range(n):
+                rid = sched.submit(len(p), max_tokens)
+                toks[rid], gen[rid] = list(p), 0
+        rid0 = min(toks)
+        while sched.num_running() or sched.num_waiting():
+            ids, offs, cnts = sched.schedule(self.prefill_token_budget)
+            if not ids:
+                raise RuntimeError("page pool too small: no waiting request can be admitted")
+            entries, sampled = [], []
+            for rid, off, cnt in zip(ids, offs, cnts):
+                last = off + cnt == len(toks[rid])
+                entries.append((sched.seq_of(rid), toks[rid][off:off + cnt], [cnt - 1] if last else []))
+                if last:
+                    sampled.append(rid)
+                self.stats["decode_tokens" if gen[rid] else "prefill_tokens"] += cnt
+            logits = self.step(entries)
+            for rid, cnt in zip(ids, cnts):
+                sched.fed(rid, cnt)
+            if not sampled:
+                continue
+            row_ids = torch.tensor([r - rid0 for r in sampled], dtype=torch.int32, device=dev)
+            row_steps = torch.tensor([gen[r] for r in sampled], dtype=torch.int32, device=dev)
+            new = native.sample(logits.contiguous(), temperature, top_p, seed, 0, row_ids, row_steps).tolist()
+            for rid, t in zip(sampled, new):
+                out[rid - rid0, gen[rid]] = t
+                gen[rid] += 1
+                if (eos_id is not None and t == eos_id) or gen[rid] >= max_tokens:
+                    sched.finish(rid)
+                else:
+                    toks[rid].append(int(t))
+                    sched.push_token(rid)
+        return out.to(dev)
