@@ -55,6 +55,10 @@ def parse():
     ap.add_argument("--reward", default="deberta-large", choices=["deberta-large", "deberta-tiny"])
     ap.add_argument("--grad-checkpointing", type=int, default=0,
                     help="1 = recompute activations like the reference (A100-40G memory saver); 0 = keep them (B200: 180 GB)")
+    ap.add_argument("--serve-bench", action="store_true",
+                    help="instead of the GRPO update: prefill / decode throughput of the hybrid step engine (Nezavik) beside the "
+                         "Qwen2 engine at equal size, and every new kernel against its roofline (bench/serve_bench.py; one GPU)")
+    ap.add_argument("--serve-quick", action="store_true", help="with --serve-bench: one small end-to-end size")
     return ap.parse_args()
 
 
@@ -73,6 +77,11 @@ def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.serve_bench:
+        sys.path.insert(0, os.path.join(ROOT, "bench"))
+        import serve_bench
+        serve_bench.main(quick=args.serve_quick)
+        return 0
 
     import torch
 

@@ -1,0 +1,227 @@
+"""Serving throughput of the hybrid step engine (Nezavik) beside the paged-KV transformer engine (Qwen2) at equal size,
+plus each new kernel against its roofline and against the like kernel of the transformer path.
+
+Run through ``python bench.py --serve-bench`` (one GPU).  Random weights, synthetic token ids.  End-to-end numbers go
+through the engines' public ``generate`` (two runs that differ by `new` generated tokens: the difference is `new` decode steps,
+the rest of the shorter run is the prompt pass); kernel numbers are CUDA-event timed after warm-up with inputs larger than L2 where the size allows.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def _time(fn, iters=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3          # seconds
+
+
+def nezavik_config(width: int, n_layers: int, vocab: int, window: int = 1024, max_positions: int = 8192):
+    from nanorlhf_b200.models.nezavik import NezavikConfig
+    H = width // 128
+    par = {"type": "parallel", "mlp": {"ff": 4 * width, "kind": "dense"},
+           "mixer": {"left": {"dim": 128, "vdim": 128, "heads": H, "kv_heads": max(1, H // 4), "mask": {"size": window},
+                              "scale": 128 ** -0.5},
+                     "right": {"conv": 4, "groups": 1, "heads": width // 64, "norm_groups": 1, "state": 128, "vdim": 64},
+                     "left_scale": 1.0, "right_scale": 1.0}}
+    dl = {"type": "delta", "mlp": {"ff": 4 * width, "kind": "dense"},
+          "mixer": {"conv": 4, "dim": 128, "vdim": 128, "heads": H, "kv_heads": H}}
+    cd = dict(dl, type="channel_delta")
+    pattern = [par, dl, cd, par]
+    return NezavikConfig.from_dict({"architecture": "Nezavik", "layers": [pattern[i % 4] for i in range(n_layers)],
+                                    "max_positions": max_positions, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width})
+
+
+def _gen_times(gen, prompts, new, base=4):
+    """(prefill seconds, seconds per decode step): generate `base` and `base + new` tokens (median of 3 after a warm-up);
+    the difference is `new` decode steps, the rest of the shorter run is the prompt pass."""
+    out = []
+    for mt in (base, base + new):
+        ts = []
+        for it in range(4):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            gen(prompts, mt)
+            torch.cuda.synchronize()
+            if it:
+                ts.append(time.perf_counter() - t0)
+        out.append(sorted(ts)[1])
+    step = max(out[1] - out[0], 1e-9) / new
+    return max(out[0] - base * step, 1e-9), step
+
+
+def end_to_end(width, n_layers, batch, prompt_len, new=128, vocab=32768):
+    from nanorlhf_b200.models.nezavik import NezavikForCausalLM
+    from nanorlhf_b200.models.qwen2 import Qwen2Config, Qwen2ForCausalLM
+    from nanorlhf_b200.sampler.hybrid_sampler import HybridSampler
+    from nanorlhf_b200.sampler.native_sampler import NativeSampler
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, vocab - 2, (batch, prompt_len), generator=g).tolist()
+    res = {"width": width, "layers": n_layers, "batch": batch, "prompt_len": prompt_len, "new_tokens": new}
+    # ---- Nezavik on the step engine ----
+    ncfg = nezavik_config(width, n_layers, vocab)
+    nez = NezavikForCausalLM.from_config(ncfg, torch.bfloat16, dev, seed=0, rank=64)
+    eng = HybridSampler(nez, dtype="bf16", max_num_seqs=batch, prefill_token_budget=16384)
+    pre, step = _gen_times(lambda p, mt: eng.generate(p, 1, 1.0, 1.0, mt, None, vocab - 1, 1), prompts, new)
+    res["nezavik"] = {"params_m": round(sum(p.numel() for p in nez.parameters()) / 1e6, 1),
+                      "prefill_tok_s": round(batch * prompt_len / pre), "decode_tok_s": round(batch / step),
+                      "decode_ms_per_step": round(step * 1e3, 3)}
+    eng.release()
+    del eng, nez
+    torch.cuda.empty_cache()
+    # ---- Qwen2 of the same width / depth on the whole-prompt engine ----
+    H = width // 128
+    qcfg = Qwen2Config(vocab_size=vocab, hidden_size=width, intermediate_size=(8 * width // 3 + 127) // 128 * 128, num_hidden_layers=n_layers,
+                       num_attention_heads=H, num_key_value_heads=max(1, H // 4), head_dim=128, tie_word_embeddings=False,
+                       max_position_embeddings=8192)
+    qw = Qwen2ForCausalLM.from_config(qcfg, torch.bfloat16, dev, seed=0)
+    qe = NativeSampler(qw, rollout_dtype="bf16", kv_cache_dtype="bf16", max_num_seqs=max(batch, 128), kv_cache_gb=8.0)
+    qe.sync_weights(force=True)
+    pre, step = _gen_times(lambda p, mt: qe.generate(p, 1, 1.0, 1.0, mt, None, vocab - 1, 1), prompts, new)
+    res["qwen2"] = {"params_m": round(sum(p.numel() for p in qw.parameters()) / 1e6, 1),
+                    "prefill_tok_s": round(batch * prompt_len / pre), "decode_tok_s": round(batch / step),
+                    "decode_ms_per_step": round(step * 1e3, 3)}
+    qe.release()
+    del qe, qw
+    torch.cuda.empty_cache()
+    return res
+
+
+def kernels(width=2048, batch=16, prompt_len=2048, window=1024, decode_batch=256, ctx=2048):
+    """Each kernel of the step engine on its own: seconds, algorithmic bytes / FLOPs, fraction of the roofline."""
+    from nanorlhf_b200 import _C
+    from nanorlhf_b200.ops import hybrid as hy, native
+    from nanorlhf_b200.sampler.hybrid_sampler import StepPlan
+    hbm, flops_peak, which = _peaks()
+    dev = torch.device("cuda:0")
+    out = {"roofline": which, "width": width}
+    H, Hkv, D = width // 128, max(1, width // 512), 128
+
+    def plan_for(B, n_new, n_old):
+        s = _C.StepScheduler((n_old + n_new + 15) // 16 * B + 8, 16, B)
+        sids = [s.open() for _ in range(B)]
+        if n_old:
+            s.plan(sids, [n_old] * B)
+        data, E, T, MB = s.plan(sids, [n_new] * B)
+        return StepPlan(torch.from_numpy(data).to(dev), E, T, MB), s
+
+    def report(name, sec, bytes_, flops=0.0, like=None):
+        floor = max(bytes_ / hbm, flops / flops_peak)
+        out[name] = {"us": round(sec * 1e6, 1), "gb_s": round(bytes_ / sec / 1e9, 1), "tflop_s": round(flops / sec / 1e12, 2),
+                     "roofline_frac": round(floor / sec, 3)}
+        if like:
+            out[name]["like"] = like
+
+    for phase, B, n_new, n_old in (("prefill", batch, prompt_len, 0), ("decode", decode_batch, 1, ctx - 1)):
+        plan, sched = plan_for(B, n_new, n_old)
+        T = plan.T
+        f32 = dict(dtype=torch.float32, device=dev)
+        # -- depth-weighted stream + norm (layer 8 of a deep model: 9 results read) vs plain fused add + RMS norm
+        nres = 9
+        results = torch.randn(nres + 1, T, width, **f32)
+        o, xp, xc = torch.randn(T, width, **f32), torch.randn(T, width, **f32), torch.empty(T, width, **f32)
+        h = torch.empty(T, width, dtype=torch.bfloat16, device=dev)
+        dw, gain = torch.rand(nres + 1, **f32), torch.ones(1, **f32)
+        sec = _time(lambda: hy.stream_norm(results, nres, o, xp, dw, gain, 1e-6, xc, h, T))
+        report(f"{phase}.stream_norm(depth 9)", sec, T * width * (4.0 * (nres + 2) + 4 * 2 + 2))
+        xb, rb, wb = torch.randn(T, width, device=dev).bfloat16(), torch.randn(T, width, device=dev).bfloat16(), torch.ones(width, device=dev).bfloat16()
+        sec = _time(lambda: native.add_rmsnorm(xb, rb, wb, 1e-6))
+        report(f"{phase}.qwen2.add_rmsnorm", sec, T * width * 2.0 * 4)
+        # -- sliding-window attention vs the transformer path's attention
+        kc = torch.randn(sched.num_free_blocks() + plan.max_blocks * B + 8, Hkv, 16, D, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        q = torch.randn(T, H * D, **f32)
+        k, v = torch.randn(T, Hkv * D, **f32), torch.randn(T, Hkv * D, **f32)
+        qw_, kw_ = torch.ones(D, **f32), torch.ones(D, **f32)
+        ao = torch.empty(T, H * D, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.qknorm_kv_write(q, k, v, qw_, kw_, 1e-6, kc, vc, plan))
+        report(f"{phase}.qknorm_kv_write", sec, T * (H + 2 * Hkv) * D * 4.0 + T * H * D * 4.0 + T * 2 * Hkv * D * 2.0)
+        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, window, D ** -0.5, 1.0, ao), iters=3, warm=1)
+        if phase == "prefill":
+            keys = sum(min(p + 1, window) for p in range(n_new)) * B
+            report(f"{phase}.window_attention(w={window})", sec, T * H * D * 6.0 + T * 2 * Hkv * D * 2.0, flops=4.0 * keys * H * D)
+        else:
+            keys = min(ctx, window)
+            report(f"{phase}.window_attention(w={window})", sec, B * keys * 2 * Hkv * D * 2.0 + T * H * D * 6.0, flops=4.0 * B * keys * H * D)
+        if phase == "prefill":
+            from nanorlhf_b200.ops.attention import attention_varlen
+            qb = torch.randn(T, H, D, device=dev).bfloat16()
+            kb, vb = torch.randn(T, Hkv, D, device=dev).bfloat16(), torch.randn(T, Hkv, D, device=dev).bfloat16()
+            cu = torch.arange(0, T + 1, n_new, dtype=torch.int32, device=dev)
+            sec = _time(lambda: attention_varlen(qb, kb, vb, cu, n_new, causal=True))
+            report("prefill.qwen2.attention_fwd(causal, full)", sec, T * (2 * H + 2 * Hkv) * D * 2.0, flops=4.0 * B * n_new * (n_new + 1) / 2 * H * D)
+        else:
+            qb = torch.randn(B, H, D, device=dev).bfloat16()
+            ctxl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+            sec = _time(lambda: native.paged_decode(qb, kc, vc, plan.block_table.contiguous(), ctxl, D ** -0.5, 1))
+            report("decode.qwen2.paged_decode(full ctx)", sec, B * ctx * 2 * Hkv * D * 2.0, flops=4.0 * B * ctx * H * D)
+        del kc, vc
+        # -- recurrent mixers (no like kernel in the transformer path)
+        Hs, P, N = width // 64, 64, 128
+        ch = Hs * P + 2 * N
+        raw, conv_w, conv_b = torch.randn(T, ch, **f32), torch.randn(ch, 4, **f32), torch.randn(ch, **f32)
+        cst, xbc = torch.zeros(B, 3, ch, **f32), torch.empty(T, ch, **f32)
+        sec = _time(lambda: hy.causal_conv(raw, conv_w, conv_b, cst, xbc, plan))
+        report(f"{phase}.causal_conv", sec, T * ch * 8.0 + B * 3 * ch * 8.0)
+        st = torch.zeros(B, Hs, N, P, **f32)
+        dt, y = torch.randn(T, Hs, **f32), torch.empty(T, Hs * P, **f32)
+        vec = torch.zeros(Hs, **f32)
+        sec = _time(lambda: hy.ssd_scan(xbc, Hs * P, Hs * P + N, dt, vec, vec, vec, st, y, plan, 1), iters=3, warm=1)
+        report(f"{phase}.ssd_scan", sec, T * (ch + Hs + Hs * P) * 4.0 + 2 * st.numel() * 4.0, flops=4.0 * T * Hs * N * P)
+        Hd, Dk, Dv = width // 128, 128, 128
+        qkv = torch.randn(T, 3 * Hd * Dk, **f32)
+        beta, dec = torch.rand(T, Hd, **f32), torch.rand(T, Hd, **f32)
+        std, od = torch.zeros(B, Hd, Dk, Dv, **f32), torch.empty(T, Hd * Dv, **f32)
+        sec = _time(lambda: hy.delta_scan(qkv, Hd * Dk, 2 * Hd * Dk, beta, dec, std, od, plan, Hd, False), iters=3, warm=1)
+        report(f"{phase}.delta_scan", sec, T * (4 * Hd * Dk + 2 * Hd) * 4.0 + 2 * std.numel() * 4.0, flops=8.0 * T * Hd * Dk * Dv)
+        gate, nw = torch.randn(T, Hd * Dv, **f32), torch.ones(Dv, **f32)
+        go = torch.empty(T, Hd * Dv, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.gated_part_rmsnorm(od, gate, nw, Dv, "silu", False, 1e-6, 1.0, go))
+        report(f"{phase}.gated_part_rmsnorm", sec, T * Hd * Dv * 10.0)
+        up = torch.randn(T, 4 * width, **f32)
+        ub = torch.empty(T, 4 * width, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.act_cols(up, ub, "relu2"))
+        report(f"{phase}.relu2", sec, T * 4 * width * 6.0)
+        gu = torch.randn(T, 8 * width, device=dev).bfloat16()
+        sec = _time(lambda: native.ext().swiglu(gu))
+        report(f"{phase}.qwen2.swiglu", sec, T * 4 * width * 6.0)
+    return out
+
+
+def main(quick: bool = False):
+    from nanorlhf_b200.ops import native
+    native.load()
+    res = {"bench": "serve", "kernels": kernels(), "end_to_end": []}
+    for width, layers, batch, plen in ((1024, 8, 32, 1024), (2048, 8, 16, 2048)) if not quick else ((1024, 4, 8, 512),):
+        res["end_to_end"].append(end_to_end(width, layers, batch, plen))
+    res["gpu_launches"] = native.launches()
+    print(json.dumps(res))
+    return res
+
+
+if __name__ == "__main__":
+    main(quick="--quick" in sys.argv)

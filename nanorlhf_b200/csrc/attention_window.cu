@@ -146,6 +146,204 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Tiled kernel: a block owns up to NQ queries that share their keys -- QT consecutive tokens x HB query heads of one
+// key/value head -- so a key row is fetched once for all of them.  Lane = key for the scores (each lane keeps NQ running
+// dot products against the queries in shared memory), lane = value columns for the output sum (softmax weights go
+// through shared memory).  Tokens of different sequences that fall into one tile are handled one run after the other.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load8(const float* p, float* o) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* o) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load4(const float* p, float* o) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* o) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+
+template <typename CT, typename OT, int NQ>
+__global__ void __launch_bounds__(kWarps * 32)
+window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
+                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_entry,
+                             const int* __restrict__ pos, int window, float scale, float out_scale, OT* __restrict__ out, long so,
+                             int T, int Hq, int Hkv, int D, int Dv, int page, int HB, int QT) {
+  extern __shared__ float sm[];
+  float* qs = sm;                                  // [NQ][D], scaled
+  float* ps = qs + NQ * D;                         // [kWarps][32][NQ]
+  float* racc = ps + kWarps * 32 * NQ;             // [kWarps][NQ][Dv]
+  float* rml = racc + kWarps * NQ * Dv;            // [kWarps][NQ][2]
+  const int g = blockIdx.y, per_g = Hq / Hkv;
+  const int h0 = g * per_g + blockIdx.z * HB;
+  const int hb = min(HB, per_g - static_cast<int>(blockIdx.z) * HB);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int t_begin = blockIdx.x * QT, t_end = min(T, t_begin + QT);
+  const bool vec8 = (D % 8) == 0;
+  float* myp = ps + w * 32 * NQ;
+  int t = t_begin;
+  while (t < t_end) {
+    const int e = tok_entry[t];
+    int tn = t + 1;
+    while (tn < t_end && tok_entry[tn] == e) ++tn;
+    const int nt = tn - t, nqs = nt * hb;
+    const int p_first = pos[t];
+    const int lo = p_first - window + 1 > 0 ? p_first - window + 1 : 0;
+    const int nkeys = p_first + nt - lo;
+    const int* bt = block_table + static_cast<long>(e) * max_blocks;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < NQ * D; idx += blockDim.x) {
+      const int qi = idx / D, c = idx - qi * D;
+      float v = 0.f;
+      if (qi < nqs) v = q[static_cast<long>(t + qi / hb) * sq + static_cast<long>(h0 + qi % hb) * D + c] * scale;
+      qs[idx] = v;
+    }
+    __syncthreads();
+    float m[NQ], l[NQ], acc[NQ][4];
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      m[i] = -INFINITY;
+      l[i] = 0.f;
+      acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    }
+    for (int base = w * 32; base < nkeys; base += kWarps * 32) {
+      const int j = lo + base + lane;
+      const bool ok = base + lane < nkeys;
+      float s[NQ];
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) s[i] = 0.f;
+      long cell = 0;
+      if (ok) {
+        cell = (static_cast<long>(bt[j / page]) * Hkv + g) * page + (j % page);
+        const CT* kr = k_cache + cell * D;
+        if (vec8) {
+          for (int c = 0; c < D; c += 8) {
+            float kv[8];
+            load8(kr + c, kv);
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) {
+              const float4 a = *reinterpret_cast<const float4*>(qs + i * D + c), b = *reinterpret_cast<const float4*>(qs + i * D + c + 4);
+              s[i] += a.x * kv[0] + a.y * kv[1] + a.z * kv[2] + a.w * kv[3] + b.x * kv[4] + b.y * kv[5] + b.z * kv[6] + b.w * kv[7];
+            }
+          }
+        } else {
+          for (int c = 0; c < D; ++c) {
+            const float kv = ld(kr, c);
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) s[i] += qs[i * D + c] * kv;
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) {
+        const int pq = p_first + i / hb;                                   // position of query i
+        const bool valid = ok && i < nqs && j <= pq && j > pq - window;
+        const float sc = valid ? s[i] : -INFINITY;
+        const float mn = fmaxf(m[i], warp_max(sc));
+        float pr = 0.f;
+        if (mn != -INFINITY) {                                              // some key of this query has been seen
+          const float corr = expf(m[i] - mn);
+          pr = valid ? expf(sc - mn) : 0.f;
+          l[i] = l[i] * corr + warp_sum(pr);
+          acc[i][0] *= corr; acc[i][1] *= corr; acc[i][2] *= corr; acc[i][3] *= corr;
+          m[i] = mn;
+        }
+        myp[lane * NQ + i] = pr;
+      }
+      __syncwarp();
+      const int cnt = nkeys - base < 32 ? nkeys - base : 32;
+      const int c0 = lane * 4;
+      for (int jj = 0; jj < cnt; ++jj) {
+        const long vr = __shfl_sync(0xffffffffu, cell, jj) * Dv;
+        float vv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (c0 < Dv) load4(v_cache + vr + c0, vv);
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+          const float pj = myp[jj * NQ + i];
+          acc[i][0] += pj * vv[0]; acc[i][1] += pj * vv[1]; acc[i][2] += pj * vv[2]; acc[i][3] += pj * vv[3];
+        }
+      }
+      __syncwarp();
+    }
+    const int c0 = lane * 4;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      if (c0 < Dv) {
+        float* d = racc + (static_cast<long>(w) * NQ + i) * Dv + c0;
+        d[0] = acc[i][0]; d[1] = acc[i][1]; d[2] = acc[i][2]; d[3] = acc[i][3];
+      }
+      if (lane == 0) {
+        rml[(w * NQ + i) * 2] = m[i];
+        rml[(w * NQ + i) * 2 + 1] = l[i];
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nqs * Dv; idx += blockDim.x) {
+      const int qi = idx / Dv, c = idx - qi * Dv;
+      float mt = -INFINITY;
+      for (int x = 0; x < kWarps; ++x) mt = fmaxf(mt, rml[(x * NQ + qi) * 2]);
+      float lt = 0.f, a = 0.f;
+      for (int x = 0; x < kWarps; ++x) {
+        const float mx = rml[(x * NQ + qi) * 2];
+        const float f = mx == -INFINITY ? 0.f : expf(mx - mt);
+        lt += f * rml[(x * NQ + qi) * 2 + 1];
+        a += f * racc[(static_cast<long>(x) * NQ + qi) * Dv + c];
+      }
+      st(out, static_cast<long>(t + qi / hb) * so + static_cast<long>(h0 + qi % hb) * Dv + c, out_scale * (a / lt));
+    }
+    t = tn;
+  }
+}
+
+template <typename CT, typename OT, int NQ>
+cudaError_t launch_tile(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+                        const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T,
+                        int Hq, int Hkv, int D, int Dv, int page, cudaStream_t s) {
+  const int per_g = Hq / Hkv;
+  const int HB = per_g < NQ ? per_g : NQ, QT = NQ / HB > 1 ? NQ / HB : 1;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(NQ) * D + kWarps * 32 * NQ + static_cast<size_t>(kWarps) * NQ * Dv + kWarps * NQ * 2);
+  if (smem > 160 * 1024) return cudaErrorInvalidValue;
+  auto kern = window_attention_tile_kernel<CT, OT, NQ>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const dim3 grid((T + QT - 1) / QT, Hkv, (per_g + HB - 1) / HB);
+  kern<<<grid, kWarps * 32, smem, s>>>(q, sq, static_cast<const CT*>(k_cache), static_cast<const CT*>(v_cache), block_table, max_blocks,
+                                       tok_entry, pos, window, scale, out_scale, static_cast<OT*>(out), so, T, Hq, Hkv, D, Dv, page, HB, QT);
+  return cudaGetLastError();
+}
+
+template <typename CT, typename OT>
+cudaError_t launch_tile_nq(int nq, const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
+                           int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out,
+                           long so, int T, int Hq, int Hkv, int D, int Dv, int page, cudaStream_t s) {
+#define NRL_WA(NQ_) return launch_tile<CT, OT, NQ_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, \
+                                                     out_scale, out, so, T, Hq, Hkv, D, Dv, page, s)
+  if (nq <= 2) NRL_WA(2);
+  if (nq <= 4) NRL_WA(4);
+  if (nq <= 8) NRL_WA(8);
+  NRL_WA(16);
+#undef NRL_WA
+}
+
 }  // namespace
 
 extern "C" {
@@ -169,9 +367,17 @@ cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, cons
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D, int Dv,
-                                 int page, cudaStream_t s) {
+                                 int page, int single_token, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
   if (Dv > 32 * kMaxDvPerLane || Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
+  if (Dv <= 128 && Dv % 4 == 0 && D <= 512) {
+    // queries per block: the heads of one key/value head for single-token steps, 16 (tokens x heads) when entries hold runs
+    const int nq = single_token ? Hq / Hkv : 16;
+    return cache_f32 ? launch_tile_nq<float, float>(nq, q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale,
+                                                    out_scale, out, so, T, Hq, Hkv, D, Dv, page, s)
+                     : launch_tile_nq<__nv_bfloat16, __nv_bfloat16>(nq, q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos,
+                                                                    window, scale, out_scale, out, so, T, Hq, Hkv, D, Dv, page, s);
+  }
   const size_t smem = sizeof(float) * (D + kWarps * Dv + 2 * kWarps);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
   const dim3 grid(T, Hq);

@@ -163,6 +163,7 @@ void qknorm_kv_write(Tensor q, const Tensor& k, const Tensor& v, const Tensor& q
 
 void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table, const Tensor& tok_entry,
                       const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out) {
+  const bool single_token = block_table.size(0) == q.size(0);
   c10::cuda::CUDAGuard guard(q.device());
   const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
   const int Dv = static_cast<int>(v_cache.size(3));
@@ -172,7 +173,7 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   check(nrl_window_attention(f32(q, "q"), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
                              i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
                              i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
-                             out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, cur_stream()),
+                             out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, cur_stream()),
         "window_attention");
 }
 

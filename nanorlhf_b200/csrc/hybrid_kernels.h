@@ -70,9 +70,9 @@ cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, cons
                                 int D, int Dv, int page, cudaStream_t s);
 
 // Sliding-window softmax attention over the paged cache: token at position p sees keys p-window+1 .. p.
-// out typed (row stride so) = out_scale * softmax(scale q.k) v.
+// out typed (row stride so) = out_scale * softmax(scale q.k) v.  single_token: every entry of the step holds one token.
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D,
-                                 int Dv, int page, cudaStream_t s);
+                                 int Dv, int page, int single_token, cudaStream_t s);
 }

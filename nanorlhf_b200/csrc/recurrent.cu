@@ -216,6 +216,225 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, long sq, int co
   for (int i = tid; i < D * Dv; i += blockDim.x) gS[i] = S[i];
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Register-resident scans (the usual sizes): thread (r, c) keeps rows r, r + R, ... of column c of the state in RPT
+// registers for the whole entry -- one global read of the state at the start, one write at the end, which is all a decoded
+// token needs -- and the next token's inputs are fetched into registers while the current token is computed.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kPre = 4;            // prefetch registers per thread
+
+template <int RPT>
+__global__ void __launch_bounds__(RPT >= 64 ? 256 : 512)
+ssd_scan_reg_kernel(const float* __restrict__ xbc, long sx, int col_b, int col_c, const float* __restrict__ dt_raw, long sd,
+                    const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                    float* __restrict__ state, float* __restrict__ y, const int* __restrict__ cu, const int* __restrict__ start,
+                    const int* __restrict__ state_slot, int heads, int groups, int N, int P, int R) {
+  extern __shared__ float sm[];
+  const int L = 2 * N + P;                       // per token: B | C | x
+  float* vec = sm;                               // [2][L]
+  float* red = sm + 2 * L;                       // [R][P]
+  const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / groups);
+  const int tid = threadIdx.x, nth = blockDim.x, r = tid / P, p = tid - r * P;
+  const bool live = r < R;
+  float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * N * P;
+  const bool carried = start[e] > 0;
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int n = r + i * R;
+    S[i] = (live && n < N && carried) ? gS[n * P + p] : 0.f;
+  }
+  const float negA = -expf(A_log[h]), dskip = Dskip[h], bias = dt_bias[h];
+  const int t0 = cu[e], t1 = cu[e + 1];
+  auto src = [&](int t, int idx) -> const float* {
+    const float* row = xbc + static_cast<long>(t) * sx;
+    return idx < N ? row + col_b + g * N + idx : idx < 2 * N ? row + col_c + g * N + (idx - N) : row + h * P + (idx - 2 * N);
+  };
+  float pre[kPre], pre_dt;
+#pragma unroll
+  for (int i = 0; i < kPre; ++i) {
+    const int idx = tid + i * nth;
+    pre[i] = idx < L ? *src(t0, idx) : 0.f;
+  }
+  pre_dt = dt_raw[static_cast<long>(t0) * sd + h];
+  for (int t = t0; t < t1; ++t) {
+    float* v = vec + ((t - t0) & 1) * L;
+#pragma unroll
+    for (int i = 0; i < kPre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < L) v[idx] = pre[i];
+    }
+    const float dt = softplus(pre_dt + bias);
+    __syncthreads();
+    if (t + 1 < t1) {
+#pragma unroll
+      for (int i = 0; i < kPre; ++i) {
+        const int idx = tid + i * nth;
+        if (idx < L) pre[i] = *src(t + 1, idx);
+      }
+      pre_dt = dt_raw[static_cast<long>(t + 1) * sd + h];
+    }
+    const float a = expf(negA * dt);
+    const float* vB = v;
+    const float* vC = v + N;
+    const float* vx = v + 2 * N;
+    if (live) {
+      const float xs = dt * vx[p];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int n = r + i * R;
+        if (n < N) {
+          S[i] = a * S[i] + vB[n] * xs;
+          acc += S[i] * vC[n];
+        }
+      }
+      red[r * P + p] = acc;
+    }
+    __syncthreads();
+    if (tid < P) {
+      float tot = 0.f;
+      for (int q = 0; q < R; ++q) tot += red[q * P + tid];
+      y[static_cast<long>(t) * heads * P + h * P + tid] = tot + dskip * vx[tid];
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int n = r + i * R;
+      if (n < N) gS[n * P + p] = S[i];
+    }
+  }
+}
+
+template <int RPT>
+__global__ void __launch_bounds__(RPT >= 64 ? 256 : 512)
+delta_scan_reg_kernel(const float* __restrict__ qkv, long sq, int col_k, int col_v, const float* __restrict__ beta,
+                      const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o, const int* __restrict__ cu,
+                      const int* __restrict__ start, const int* __restrict__ state_slot, int heads, int kv_heads, int D, int Dv,
+                      int per_channel, int R) {
+  extern __shared__ float sm[];
+  const int L = 3 * D;                           // per token: q | k | decay per row
+  float* vec = sm;                               // [2][L]
+  float* red = sm + 2 * L;                       // [2][R][Dv]
+  float* rkq = red + 2 * R * Dv;                 // [R]
+  const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / kv_heads);
+  const int tid = threadIdx.x, nth = blockDim.x, r = tid / Dv, c = tid - r * Dv;
+  const bool live = r < R;
+  float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * D * Dv;
+  const bool carried = start[e] > 0;
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int d = r + i * R;
+    S[i] = (live && d < D && carried) ? gS[d * Dv + c] : 0.f;
+  }
+  const int t0 = cu[e], t1 = cu[e + 1];
+  const int nd = per_channel ? heads * D : heads;
+  auto src = [&](int t, int idx) -> const float* {
+    const float* row = qkv + static_cast<long>(t) * sq;
+    return idx < D ? row + g * D + idx
+           : idx < 2 * D ? row + col_k + g * D + (idx - D)
+                         : decay + static_cast<long>(t) * nd + (per_channel ? h * D + (idx - 2 * D) : h);
+  };
+  float pre[kPre], pre_v = 0.f, pre_beta;
+#pragma unroll
+  for (int i = 0; i < kPre; ++i) {
+    const int idx = tid + i * nth;
+    pre[i] = idx < L ? *src(t0, idx) : 0.f;
+  }
+  if (live) pre_v = qkv[static_cast<long>(t0) * sq + col_v + h * Dv + c];
+  pre_beta = beta[static_cast<long>(t0) * heads + h];
+  for (int t = t0; t < t1; ++t) {
+    float* v = vec + ((t - t0) & 1) * L;
+#pragma unroll
+    for (int i = 0; i < kPre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < L) v[idx] = pre[i];
+    }
+    const float v_cur = pre_v, b_cur = pre_beta;
+    __syncthreads();
+    if (t + 1 < t1) {
+#pragma unroll
+      for (int i = 0; i < kPre; ++i) {
+        const int idx = tid + i * nth;
+        if (idx < L) pre[i] = *src(t + 1, idx);
+      }
+      if (live) pre_v = qkv[static_cast<long>(t + 1) * sq + col_v + h * Dv + c];
+      pre_beta = beta[static_cast<long>(t + 1) * heads + h];
+    }
+    const float* vq = v;
+    const float* vk = v + D;
+    const float* vg = v + 2 * D;
+    if (live) {
+      float pk = 0.f, pq = 0.f, pkq = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int d = r + i * R;
+        if (d < D) {
+          const float sv = vg[d] * S[i];
+          S[i] = sv;
+          pk += sv * vk[d];
+          pq += sv * vq[d];
+          if (c == 0) pkq += vk[d] * vq[d];
+        }
+      }
+      red[r * Dv + c] = pk;
+      red[(R + r) * Dv + c] = pq;
+      if (c == 0) rkq[r] = pkq;
+    }
+    __syncthreads();
+    if (live) {
+      float sk = 0.f, sq_ = 0.f, kq = 0.f;
+      for (int x = 0; x < R; ++x) {
+        sk += red[x * Dv + c];
+        sq_ += red[(R + x) * Dv + c];
+        kq += rkq[x];
+      }
+      const float u = b_cur * (v_cur - sk);
+      if (r == 0) o[static_cast<long>(t) * heads * Dv + h * Dv + c] = sq_ + u * kq;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int d = r + i * R;
+        if (d < D) S[i] += vk[d] * u;
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int d = r + i * R;
+      if (d < D) gS[d * Dv + c] = S[i];
+    }
+  }
+}
+
+// rows per thread / row groups for a state of `rows` x `cols`: as many row groups as 512 threads allow (256 when a thread
+// holds 64 rows), at most 64 rows per thread, and enough threads to fetch a token's inputs with kPre loads each
+bool pick_reg_layout(int cols, int rows, int per_token, int* R_out, int* rpt_out, int* threads_out) {
+  if (cols > 512) return false;
+  int R = 512 / cols;
+  if (R > rows) R = rows;
+  if (R < 1) return false;
+  int need = (rows + R - 1) / R;
+  if (need > 32) {
+    R = 256 / cols;
+    if (R > rows) R = rows;
+    if (R < 1) return false;
+    need = (rows + R - 1) / R;
+    if (need > 64) return false;
+    if (need <= 32) need = 33;                      // stays in the 64-row variant, whose blocks have 256 threads
+  }
+  const int rpt = need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : need <= 32 ? 32 : 64;
+  int threads = ((cols * R + 31) / 32) * 32;
+  const int for_loads = (((per_token + kPre - 1) / kPre + 31) / 32) * 32;
+  if (threads < for_loads) threads = for_loads;
+  if (threads > (rpt == 64 ? 256 : 512)) return false;
+  *R_out = R; *rpt_out = rpt; *threads_out = threads;
+  return true;
+}
+
 int pick_rows(int cols, int rows) {
   // threads = cols * R <= 512, R <= rows
   int R = 512 / cols;
@@ -254,6 +473,21 @@ cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const 
                          const int* state_slot, int E, int heads, int groups, int N, int P, cudaStream_t s) {
   if (E <= 0) return cudaSuccess;
   if (P > 512 || heads % groups != 0) return cudaErrorInvalidValue;
+  {
+    int R, rpt, threads;
+    const size_t smem_reg = sizeof(float) * (2 * (2 * static_cast<size_t>(N) + P) + 512);
+    if (pick_reg_layout(P, N, 2 * N + P, &R, &rpt, &threads) && smem_reg <= 48 * 1024) {
+      const size_t smem = sizeof(float) * (2 * (2 * static_cast<size_t>(N) + P) + static_cast<size_t>(R) * P);
+#define NRL_SSD(RPT_)                                                                                                              \
+  if (rpt == RPT_) {                                                                                                               \
+    ssd_scan_reg_kernel<RPT_><<<dim3(E, heads), threads, smem, s>>>(xbc, sx, col_b, col_c, dt_raw, sd, dt_bias, A_log, Dskip, state, y, \
+                                                                    cu, start, state_slot, heads, groups, N, P, R);                \
+    return cudaGetLastError();                                                                                                     \
+  }
+      NRL_SSD(4) NRL_SSD(8) NRL_SSD(16) NRL_SSD(32) NRL_SSD(64)
+#undef NRL_SSD
+    }
+  }
   const int R = pick_rows(P, N);
   const int threads = ((P * R + 31) / 32) * 32;
   const size_t smem = sizeof(float) * (static_cast<size_t>(N) * P + 2 * N + P + static_cast<size_t>(R) * P);
@@ -283,6 +517,21 @@ cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, cons
                            int Dv, int per_channel, cudaStream_t s) {
   if (E <= 0) return cudaSuccess;
   if (Dv > 512 || heads % kv_heads != 0) return cudaErrorInvalidValue;
+  {
+    int R, rpt, threads;
+    const size_t smem_reg = sizeof(float) * (6 * static_cast<size_t>(D) + 2 * 512 + 64);
+    if (pick_reg_layout(Dv, D, 3 * D, &R, &rpt, &threads) && smem_reg <= 48 * 1024) {
+      const size_t smem = sizeof(float) * (6 * static_cast<size_t>(D) + 2 * static_cast<size_t>(R) * Dv + R);
+#define NRL_DELTA(RPT_)                                                                                                            \
+  if (rpt == RPT_) {                                                                                                               \
+    delta_scan_reg_kernel<RPT_><<<dim3(E, heads), threads, smem, s>>>(qkv, sq, col_k, col_v, beta, decay, state, o, cu, start,       \
+                                                                      state_slot, heads, kv_heads, D, Dv, per_channel, R);         \
+    return cudaGetLastError();                                                                                                     \
+  }
+      NRL_DELTA(4) NRL_DELTA(8) NRL_DELTA(16) NRL_DELTA(32) NRL_DELTA(64)
+#undef NRL_DELTA
+    }
+  }
   const int R = pick_rows(Dv, D);
   const int threads = ((Dv * R + 31) / 32) * 32;
   const size_t smem = sizeof(float) * (static_cast<size_t>(D) * Dv + 3 * D + 2 * static_cast<size_t>(R) * Dv + 1);

@@ -329,7 +329,8 @@ class StepScheduler {
   int block_size() const { return bm_.block_size(); }
 
   // Append counts[i] tokens to sids[i] (each sequence at most once per step) and describe the step.
-  StepPlan plan(const std::vector<int>& sids, const std::vector<int>& counts) {
+  // `min_blocks` pads the block table's width (a captured CUDA graph wants it fixed while sequences grow).
+  StepPlan plan(const std::vector<int>& sids, const std::vector<int>& counts, int min_blocks = 0) {
     if (sids.size() != counts.size()) throw std::invalid_argument("plan: sids and counts differ in length");
     const int E = static_cast<int>(sids.size()), bs = bm_.block_size();
     int T = 0, need = 0, unreserved_need = 0;
@@ -359,6 +360,7 @@ class StepScheduler {
       }
       p.max_blocks = std::max(p.max_blocks, static_cast<int>(q.blocks.size()));
     }
+    p.max_blocks = std::max(p.max_blocks, min_blocks);
     const int MB = p.max_blocks;
     p.data.assign(static_cast<size_t>(T) + (E + 1) + 3 * static_cast<size_t>(T) + 2 * E + static_cast<size_t>(E) * MB, 0);
     int* cu = p.data.data() + T;
@@ -509,12 +511,12 @@ void bind_runtime(py::module_& m) {
       .def("num_free_slots", &StepScheduler::num_free_slots)
       .def("num_open", &StepScheduler::num_open)
       .def("block_size", &StepScheduler::block_size)
-      .def("plan", [](StepScheduler& self, const std::vector<int>& sids, const std::vector<int>& counts) {
-             StepPlan p = self.plan(sids, counts);
+      .def("plan", [](StepScheduler& self, const std::vector<int>& sids, const std::vector<int>& counts, int min_blocks) {
+             StepPlan p = self.plan(sids, counts, min_blocks);
              py::array_t<int> out(static_cast<py::ssize_t>(p.data.size()));
              std::copy(p.data.begin(), p.data.end(), out.mutable_data());
              return py::make_tuple(out, p.E, p.T, p.max_blocks);
-           }, py::arg("seq_ids"), py::arg("counts"))
+           }, py::arg("seq_ids"), py::arg("counts"), py::arg("min_blocks") = 0)
       .def("submit", &StepScheduler::submit)
       .def("schedule", &StepScheduler::schedule)
       .def("fed", &StepScheduler::fed)

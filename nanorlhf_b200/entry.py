@@ -64,9 +64,14 @@ def load_tokenizer_and_policies(args, dtype=torch.bfloat16, device=None):
     if tokenizer.pad_token_id is None or tokenizer.pad_token_id == tokenizer.eos_token_id:
         tokenizer.add_special_tokens({"pad_token": "[PAD]"})
     tokenizer.padding_side = "left"
-    if local:
-        policy = Qwen2ForCausalLM.from_pretrained(path, dtype, device)
-        ref_policy = Qwen2ForCausalLM.from_pretrained(path, dtype, device)
+    if local:                                   # the class is chosen by the checkpoint's config.json (models/registry.py)
+        from .models.registry import load_model, sampler_kind
+        policy = load_model(path, dtype, device)
+        if sampler_kind(policy) == "hybrid":
+            raise NotImplementedError(
+                f"{type(policy).__name__} is served for generation only (step engine: sampler.engine.generate, "
+                "python -m nanorlhf_b200.sampler, bin/trace_run); the RL trainers need a model family with a training forward")
+        ref_policy = load_model(path, dtype, device)
     else:
         cfg = _shape_for(path, len(tokenizer))
         cfg.name_or_path = path

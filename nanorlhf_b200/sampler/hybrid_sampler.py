@@ -67,7 +67,8 @@ class HybridSampler:
     PAGE = 16
 
     def __init__(self, model, dtype: str = "bf16", kv_block_size: int = 16, max_num_seqs: int = 64, pool_tokens: Optional[int] = None,
-                 prefill_token_budget: int = 8192, gemm: str = "tc", rollout_dtype: Optional[str] = None, **_unused):
+                 prefill_token_budget: int = 8192, gemm: str = "tc", rollout_dtype: Optional[str] = None,
+                 use_cuda_graph: bool = True, **_unused):
         if kv_block_size != self.PAGE:
             raise ValueError("KV pages hold 16 tokens")
         native.load()
@@ -95,7 +96,11 @@ class HybridSampler:
         self.layers: List[_Layer] = []
         self.sched = None
         self.num_blocks = 0
-        self.stats = {"steps": 0, "tokens": 0, "decode_tokens": 0, "prefill_tokens": 0}
+        self.stats = {"steps": 0, "tokens": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0}
+        self.use_cuda_graph = use_cuda_graph
+        self._graphs: Dict[tuple, tuple] = {}             # (entries, block-table width) -> (graph, plan buffer, logits, launches)
+        self._graph_seen: set = set()
+        self._bt_width = 0                                # generate() fixes the block-table width so decode steps can be replayed
         self._build_arena()
 
     # ------------------------------------------------------------------------------------------
@@ -205,6 +210,8 @@ class HybridSampler:
                 M.k_cache, M.v_cache, M.conv_state, M.state = pl
 
     def release(self):
+        self._graphs.clear()
+        self._graph_seen.clear()
         self.layers, self.sched, self.num_blocks = [], None, 0
 
     # ------------------------------------------------------------------------------------------
@@ -231,6 +238,8 @@ class HybridSampler:
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
                     M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
         self.num_blocks, self.num_slots = n, num_slots
+        self._graphs.clear()                              # captured graphs hold the old pool's addresses
+        self._graph_seen.clear()
         self.sched = _C.StepScheduler(n, self.PAGE, num_slots)
 
     def open(self, reserve_tokens: int = 0) -> int:
@@ -261,16 +270,44 @@ class HybridSampler:
         Returns float32 logits [wanted, vocab] in entry order."""
         sids = [int(e[0]) for e in entries]
         counts = [len(e[1]) for e in entries]
-        data, E, T, MB = self.sched.plan(sids, counts)
+        data, E, T, MB = self.sched.plan(sids, counts, self._bt_width)
         o, rows = 0, []
         for (_sid, toks, want), c in zip(entries, counts):
             data[o:o + c] = np.asarray(toks, dtype=np.int32)
             rows += [o + int(j) for j in want]
             o += c
-        plan = StepPlan(torch.from_numpy(data).to(self.device), E, T, MB)
         self.stats["steps"] += 1
         self.stats["tokens"] += T
+        if self.use_cuda_graph and self._bt_width and T == E and len(rows) == T:
+            return self._decode_step_graphed(data, E, MB)
+        plan = StepPlan(torch.from_numpy(data).to(self.device), E, T, MB)
         return self._forward(plan, rows)
+
+    def _decode_step_graphed(self, data, E: int, MB: int) -> torch.Tensor:
+        """A step of single tokens (one per sequence, all logits wanted) has the same launches whatever the sequences hold:
+        the second time a batch size shows up its launches are captured into a CUDA graph, from then on a step is one copy
+        of the plan and one replay.  (The first time runs eagerly: it is a real step, and it warms up lazy kernel setup.)"""
+        key = (E, MB)
+        entry = self._graphs.get(key)
+        if entry is None:
+            if key not in self._graph_seen:
+                self._graph_seen.add(key)
+                return self._forward(StepPlan(torch.from_numpy(data).to(self.device), E, E, MB), list(range(E)))
+            buf = torch.from_numpy(data).to(self.device)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            n0 = native.launches()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                logits = self._forward(StepPlan(buf, E, E, MB), list(range(E)))
+            if len(self._graphs) >= 16:
+                self._graphs.pop(next(iter(self._graphs)))
+            entry = self._graphs[key] = (g, buf, logits, native.launches() - n0)
+        else:
+            entry[1].copy_(torch.from_numpy(data))
+        entry[0].replay()
+        native._count(entry[3])
+        self.stats["graph_replays"] += 1
+        return entry[2]
 
     def _forward(self, plan: StepPlan, rows: List[int]) -> torch.Tensor:
         cfg, dev, wd = self.cfg, self.device, self.wdtype
@@ -369,6 +406,7 @@ class HybridSampler:
         if self.sched is None or self.sched.num_open() or self.num_blocks * self.PAGE < need or self.num_slots < slots:
             self.reset_pool(need, slots)
         sched = self.sched
+        self._bt_width = max(per_seq) // self.PAGE        # fixed width: decode steps of one batch size share a CUDA graph
         toks: Dict[int, List[int]] = {}
         gen: Dict[int, int] = {}
         for p in prompts:
@@ -394,7 +432,7 @@ class HybridSampler:
                 continue
             row_ids = torch.tensor([r - rid0 for r in sampled], dtype=torch.int32, device=dev)
             row_steps = torch.tensor([gen[r] for r in sampled], dtype=torch.int32, device=dev)
-            new = native.sample(logits.contiguous(), temperature, top_p, seed, 0, row_ids, row_steps).tolist()
+            new = native.sample(logits, temperature, top_p, seed, 0, row_ids, row_steps).tolist()   # rows keep their padded stride
             for rid, t in zip(sampled, new):
                 out[rid - rid0, gen[rid]] = t
                 gen[rid] += 1
@@ -403,4 +441,5 @@ class HybridSampler:
                 else:
                     toks[rid].append(int(t))
                     sched.push_token(rid)
+        self._bt_width = 0
         return out.to(dev)
