@@ -129,8 +129,10 @@ def kernels(width=2048, batch=16, prompt_len=2048, window=1024, decode_batch=256
         data, E, T, MB = s.plan(sids, [n_new] * B)
         return StepPlan(torch.from_numpy(data).to(dev), E, T, MB), s
 
-    def report(name, sec, bytes_, flops=0.0, like=None):
-        floor = max(bytes_ / hbm, flops / flops_peak)
+    fp32_peak = 148 * 128 * 2 * 1.9e9              # FMA lanes x 2 x clock: the float32 scans cannot use the tensor cores
+
+    def report(name, sec, bytes_, flops=0.0, like=None, fp32=False):
+        floor = max(bytes_ / hbm, flops / (fp32_peak if fp32 else flops_peak))
         out[name] = {"us": round(sec * 1e6, 1), "gb_s": round(bytes_ / sec / 1e9, 1), "tflop_s": round(flops / sec / 1e12, 2),
                      "roofline_frac": round(floor / sec, 3)}
         if like:
@@ -160,13 +162,15 @@ def kernels(width=2048, batch=16, prompt_len=2048, window=1024, decode_batch=256
         ao = torch.empty(T, H * D, dtype=torch.bfloat16, device=dev)
         sec = _time(lambda: hy.qknorm_kv_write(q, k, v, qw_, kw_, 1e-6, kc, vc, plan))
         report(f"{phase}.qknorm_kv_write", sec, T * (H + 2 * Hkv) * D * 4.0 + T * H * D * 4.0 + T * 2 * Hkv * D * 2.0)
-        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, window, D ** -0.5, 1.0, ao), iters=3, warm=1)
-        if phase == "prefill":
-            keys = sum(min(p + 1, window) for p in range(n_new)) * B
-            report(f"{phase}.window_attention(w={window})", sec, T * H * D * 6.0 + T * 2 * Hkv * D * 2.0, flops=4.0 * keys * H * D)
-        else:
-            keys = min(ctx, window)
-            report(f"{phase}.window_attention(w={window})", sec, B * keys * 2 * Hkv * D * 2.0 + T * H * D * 6.0, flops=4.0 * B * keys * H * D)
+        for impl in ("auto", "tile", "mma"):
+            sec = _time(lambda: hy.window_attention(q, kc, vc, plan, window, D ** -0.5, 1.0, ao, impl=impl), iters=3, warm=1)
+            name = f"{phase}.window_attention(w={window})" + ("" if impl == "auto" else f"[{impl}]")
+            if phase == "prefill":
+                keys = sum(min(p + 1, window) for p in range(n_new)) * B
+                report(name, sec, T * H * D * 6.0 + T * 2 * Hkv * D * 2.0, flops=4.0 * keys * H * D)
+            else:
+                keys = min(ctx, window)
+                report(name, sec, B * keys * 2 * Hkv * D * 2.0 + T * H * D * 6.0, flops=4.0 * B * keys * H * D)
         if phase == "prefill":
             from nanorlhf_b200.ops.attention import attention_varlen
             qb = torch.randn(T, H, D, device=dev).bfloat16()
@@ -190,14 +194,18 @@ def kernels(width=2048, batch=16, prompt_len=2048, window=1024, decode_batch=256
         st = torch.zeros(B, Hs, N, P, **f32)
         dt, y = torch.randn(T, Hs, **f32), torch.empty(T, Hs * P, **f32)
         vec = torch.zeros(Hs, **f32)
-        sec = _time(lambda: hy.ssd_scan(xbc, Hs * P, Hs * P + N, dt, vec, vec, vec, st, y, plan, 1), iters=3, warm=1)
-        report(f"{phase}.ssd_scan", sec, T * (ch + Hs + Hs * P) * 4.0 + 2 * st.numel() * 4.0, flops=4.0 * T * Hs * N * P)
+        for impl in ("auto", "rows"):
+            sec = _time(lambda: hy.ssd_scan(xbc, Hs * P, Hs * P + N, dt, vec, vec, vec, st, y, plan, 1, impl=impl), iters=3, warm=1)
+            report(f"{phase}.ssd_scan" + ("" if impl == "auto" else f"[{impl}]"), sec,
+                   T * (ch + Hs + Hs * P) * 4.0 + 2 * st.numel() * 4.0, flops=6.0 * T * Hs * N * P, fp32=True)
         Hd, Dk, Dv = width // 128, 128, 128
         qkv = torch.randn(T, 3 * Hd * Dk, **f32)
         beta, dec = torch.rand(T, Hd, **f32), torch.rand(T, Hd, **f32)
         std, od = torch.zeros(B, Hd, Dk, Dv, **f32), torch.empty(T, Hd * Dv, **f32)
-        sec = _time(lambda: hy.delta_scan(qkv, Hd * Dk, 2 * Hd * Dk, beta, dec, std, od, plan, Hd, False), iters=3, warm=1)
-        report(f"{phase}.delta_scan", sec, T * (4 * Hd * Dk + 2 * Hd) * 4.0 + 2 * std.numel() * 4.0, flops=8.0 * T * Hd * Dk * Dv)
+        for impl in ("auto", "rows"):
+            sec = _time(lambda: hy.delta_scan(qkv, Hd * Dk, 2 * Hd * Dk, beta, dec, std, od, plan, Hd, False, impl=impl), iters=3, warm=1)
+            report(f"{phase}.delta_scan" + ("" if impl == "auto" else f"[{impl}]"), sec,
+                   T * (4 * Hd * Dk + 2 * Hd) * 4.0 + 2 * std.numel() * 4.0, flops=8.0 * T * Hd * Dk * Dv, fp32=True)
         gate, nw = torch.randn(T, Hd * Dv, **f32), torch.ones(Dv, **f32)
         go = torch.empty(T, Hd * Dv, dtype=torch.bfloat16, device=dev)
         sec = _time(lambda: hy.gated_part_rmsnorm(od, gate, nw, Dv, "silu", False, 1e-6, 1.0, go))

@@ -1,0 +1,323 @@
+// Sliding-window attention for prompt portions on the tensor cores, reading the 16-token bf16 pages in place.
+//
+// A block owns 64 query rows that share one key/value head -- QT consecutive tokens x HB query heads -- as four warps of 16
+// rows, and walks the keys its rows can see in blocks of 64 (four pages), double buffered through shared memory with
+// cp.async.  Per block:  S = Q K^T (bf16 operands, float accumulators), scores scaled and masked in float (key j is seen
+// by the query at position p when p - window < j <= p), online softmax in float (base 2, ex2.approx), P rounded to bf16 only as the operand
+// of O += P V (float accumulators).  Query / key size D and value size Dv are runtime values; the templates fix the padded
+// sizes (multiples of 32 up to 128), the padding is zero-filled in shared memory.  Tokens of different sequences that fall
+// into one tile are handled one run after the other over the same accumulators (a row belongs to one run only).
+// Compiled WITHOUT fast-math.
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "hybrid_kernels.h"
+
+namespace {
+
+constexpr int kBM = 64;        // query rows per block
+constexpr int kBN = 64;        // keys per block of the walk
+constexpr int kThreads = 128;
+constexpr int kPad = 8;        // bf16 elements appended to a shared-memory row (ldmatrix without bank conflicts)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+
+// 2^x on the special-function unit (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// one 64-key block of K or V into shared memory: rows = keys kb .. kb + 63 of the sequence, `width` real columns of `wp`
+__device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int* bt, int Hkv, int g, int kb,
+                                              int hi, int width, int wp) {
+  const int chunks = wp / 8, ld = wp + kPad;
+  for (int idx = threadIdx.x; idx < kBN * chunks; idx += kThreads) {
+    const int key = idx / chunks, ch = idx - key * chunks;
+    const int j = kb + key;
+    __nv_bfloat16* d = dst + key * ld + ch * 8;
+    if (j <= hi && ch * 8 < width) {
+      const long cell = (static_cast<long>(bt[j >> 4]) * Hkv + g) * 16 + (j & 15);
+      cp_async16(smem_u32(d), cache + cell * width + ch * 8);
+    } else {
+      *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+template <int KS, int NV>      // padded D = 16 KS, padded Dv = 16 NV
+__global__ void __launch_bounds__(kThreads)
+window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
+                            const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+                            const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale, float out_scale,
+                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT) {
+  constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kBM][LDK]
+  __nv_bfloat16* sK = sQ + kBM * LDK;                                         // [2][kBN][LDK]
+  __nv_bfloat16* sV = sK + 2 * kBN * LDK;                                     // [2][kBN][LDV]
+  const int g = blockIdx.y, per_g = Hq / Hkv, h0 = g * per_g + blockIdx.z * HB;
+  const int hb = min(HB, per_g - static_cast<int>(blockIdx.z) * HB);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+  const int t_begin = blockIdx.x * QT, t_end = min(T, t_begin + QT);
+
+  // ---- queries: float -> bf16 into shared memory (zero rows / columns where there is no query), then A fragments ----
+  for (int idx = threadIdx.x; idx < kBM * DP; idx += kThreads) {
+    const int r = idx / DP, c = idx - r * DP;
+    const int tt = t_begin + r / HB, hh = r % HB;
+    float v = 0.f;
+    if (r < QT * HB && tt < t_end && hh < hb && c < D) v = q[static_cast<long>(tt) * sq + static_cast<long>(h0 + hh) * D + c];
+    sQ[r * LDK + c] = __float2bfloat16_rn(v);
+  }
+  __syncthreads();
+  uint32_t qf[KS][4];
+  {
+    const int m = lane >> 3, rr = w * 16 + (m & 1) * 8 + (lane & 7);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) ldsm_x4(smem_u32(sQ + rr * LDK + ks * 16 + (m >> 1) * 8), qf[ks]);
+  }
+  // the two rows of this thread: w*16 + gq and w*16 + gq + 8
+  int row_t[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int r = w * 16 + gq + hf * 8;
+    row_t[hf] = t_begin + r / HB;
+    row_ok[hf] = r < QT * HB && row_t[hf] < t_end && (r % HB) < hb;
+  }
+  // tokens that the rows of this warp cover (to skip key blocks none of them sees)
+  const int wt_lo = t_begin + (w * 16) / HB, wt_hi = min(t_end - 1, t_begin + (w * 16 + 15) / HB);
+
+  float o[2 * NV][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // running maxima live in the log2 domain
+  const float sl2 = scale * 1.4426950408889634f;
+
+  int t = t_begin;
+  while (t < t_end) {
+    const int e = tok_entry[t];
+    int tn = t + 1;
+    while (tn < t_end && tok_entry[tn] == e) ++tn;
+    const int p_first = pos[t];
+    const int lo = max(0, p_first - window + 1), hi = p_first + (tn - t) - 1;
+    const int* bt = block_table + static_cast<long>(e) * max_blocks;
+    const int kb0 = (lo / kBN) * kBN;
+    const int nblk = (hi - kb0) / kBN + 1;
+    // positions of this thread's rows inside the run (or "not in this run")
+    int pq[2];
+    bool act[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      act[hf] = row_ok[hf] && row_t[hf] >= t && row_t[hf] < tn;
+      pq[hf] = p_first + (row_t[hf] - t);
+    }
+    // keys the warp's rows of this run can see: [wlo, whi]
+    const int wa = max(wt_lo, t), wb = min(wt_hi, tn - 1);
+    const bool warp_in = wa <= wb;
+    const bool warp_full = wt_lo >= t && wt_hi < tn;       // every row of the warp that holds a query belongs to this run
+    const int whi = p_first + (wb - t), wlo = p_first + (wa - t) - window + 1;
+
+    __syncthreads();                                       // the previous run's last block has been consumed
+    load_kv_block(sK, k_cache, bt, Hkv, g, kb0, hi, D, DP);
+    load_kv_block(sV, v_cache, bt, Hkv, g, kb0, hi, Dv, DVP);
+    cp_commit();
+    for (int ib = 0; ib < nblk; ++ib) {
+      const int kb = kb0 + ib * kBN, buf = ib & 1;
+      if (ib + 1 < nblk) {
+        load_kv_block(sK + (buf ^ 1) * kBN * LDK, k_cache, bt, Hkv, g, kb + kBN, hi, D, DP);
+        load_kv_block(sV + (buf ^ 1) * kBN * LDV, v_cache, bt, Hkv, g, kb + kBN, hi, Dv, DVP);
+        cp_commit();
+        cp_wait<1>();
+      } else {
+        cp_wait<0>();
+      }
+      __syncthreads();
+      if (warp_in && kb <= whi && kb + kBN - 1 >= wlo) {
+        const __nv_bfloat16* bK = sK + buf * kBN * LDK;
+        const __nv_bfloat16* bV = sV + buf * kBN * LDV;
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        {
+          const int m = lane >> 3;
+          const int krow = (m >> 1) * 8 + (lane & 7), kcol = (m & 1) * 8;
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+              uint32_t b[4];
+              ldsm_x4(smem_u32(bK + (np * 16 + krow) * LDK + ks * 16 + kcol), b);
+              mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+              mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+          }
+        }
+        // scale (log2 domain), mask, online softmax (float).  A block that every row of the warp sees whole needs no mask.
+        const bool interior = warp_full && kb + kBN - 1 <= p_first + (wt_lo - t) && kb > whi - window;
+        float mx[2] = {-INFINITY, -INFINITY};
+        if (interior) {
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              s[n][i] *= sl2;
+              mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int hf = i >> 1, j = kb + n * 8 + 2 * tq + (i & 1);
+              const bool valid = act[hf] && j <= pq[hf] && j > pq[hf] - window;
+              const float sc = valid ? s[n][i] * sl2 : -INFINITY;
+              s[n][i] = sc;
+              mx[hf] = fmaxf(mx[hf], sc);
+            }
+          }
+        }
+        float corr[2], m_sub[2];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+          mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+          const float mn = fmaxf(m_run[hf], mx[hf]);
+          corr[hf] = mn == -INFINITY ? 1.f : ex2(m_run[hf] - mn);            // nothing seen yet: nothing to rescale
+          m_run[hf] = mn;
+          m_sub[hf] = mn == -INFINITY ? 0.f : mn;                             // 2^(-inf - 0) = 0 for a row without keys so far
+          l_run[hf] *= corr[hf];
+        }
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int hf = i >> 1;
+            const float pr = ex2(s[n][i] - m_sub[hf]);
+            s[n][i] = pr;
+            l_run[hf] += pr;                                                  // per-thread part of the row sum
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * NV; ++i) {
+          o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        {
+          const int m = lane >> 3;
+          const int vrow = (m & 1) * 8 + (lane & 7), vcol = (m >> 1) * 8;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int nv = 0; nv < NV; ++nv) {
+              uint32_t b[4];
+              ldsm_x4_t(smem_u32(bV + (kk * 16 + vrow) * LDV + nv * 16 + vcol), b);
+              mma_bf16(o[2 * nv], pa, b[0], b[1]);
+              mma_bf16(o[2 * nv + 1], pa, b[2], b[3]);
+            }
+          }
+        }
+      }
+      __syncthreads();                                     // all warps are done with `buf` before it is filled again
+    }
+    t = tn;
+  }
+  // ---- out = out_scale * O / l ----
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    float l = l_run[hf];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (!row_ok[hf]) continue;
+    const int r = w * 16 + gq + hf * 8;
+    __nv_bfloat16* dst = out + static_cast<long>(row_t[hf]) * so + static_cast<long>(h0 + r % HB) * Dv;
+    const float f = out_scale / l;
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i) {
+      const int c = i * 8 + 2 * tq;
+      if (c < Dv) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(o[i][2 * hf] * f, o[i][2 * hf + 1] * f);
+    }
+  }
+}
+
+template <int KS, int NV>
+cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+                   const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T, int Hq,
+                   int Hkv, int D, int Dv, int single_token, cudaStream_t s) {
+  const int per_g = Hq / Hkv;
+  // a step of single tokens: one token per block (every token walks its own sequence; more blocks, shorter walks)
+  const int HB = per_g < kBM ? per_g : kBM, QT = single_token ? 1 : kBM / HB;
+  constexpr size_t smem = sizeof(__nv_bfloat16) * (static_cast<size_t>(kBM) * (16 * KS + kPad) + 2 * kBN * (16 * KS + kPad) +
+                                                   2 * kBN * (16 * NV + kPad));
+  auto kern = window_attention_mma_kernel<KS, NV>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const dim3 grid((T + QT - 1) / QT, Hkv, (per_g + HB - 1) / HB);
+  kern<<<grid, kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
+                                    block_table, max_blocks, tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so,
+                                    T, Hq, Hkv, D, Dv, HB, QT);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int D, int Dv, int page) {
+  return page == 16 && Hkv > 0 && Hq % Hkv == 0 && D % 8 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && so % 2 == 0 &&
+         reinterpret_cast<uintptr_t>(out) % 4 == 0;
+}
+
+cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
+                                     int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
+                                     void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
+                                     cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (!nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) || window < 1) return cudaErrorInvalidValue;
+  const int ks = D <= 32 ? 2 : D <= 64 ? 4 : 8, nv = Dv <= 32 ? 2 : Dv <= 64 ? 4 : 8;
+#define NRL_WM(KS_, NV_)                                                                                                         \
+  if (ks == KS_ && nv == NV_)                                                                                                    \
+    return launch<KS_, NV_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so, T, Hq, \
+                            Hkv, D, Dv, single_token, s);
+  NRL_WM(2, 2) NRL_WM(2, 4) NRL_WM(2, 8) NRL_WM(4, 2) NRL_WM(4, 4) NRL_WM(4, 8) NRL_WM(8, 2) NRL_WM(8, 4) NRL_WM(8, 8)
+#undef NRL_WM
+  return cudaErrorInvalidValue;
+}
+
+}  // extern "C"

@@ -100,7 +100,8 @@ void causal_conv(const Tensor& in, const Tensor& w, const c10::optional<Tensor>&
 }
 
 void ssd_scan(const Tensor& xbc, int64_t col_b, int64_t col_c, const Tensor& dt_raw, const Tensor& dt_bias, const Tensor& A_log,
-              const Tensor& Dskip, Tensor state, Tensor y, const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t groups) {
+              const Tensor& Dskip, Tensor state, Tensor y, const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t groups,
+              int64_t impl) {
   c10::cuda::CUDAGuard guard(y.device());
   TORCH_CHECK(state.dim() == 4 && state.is_contiguous(), "ssd_scan: state [slots, heads, N, P]");
   const int heads = static_cast<int>(state.size(1)), N = static_cast<int>(state.size(2)), P = static_cast<int>(state.size(3));
@@ -112,7 +113,7 @@ void ssd_scan(const Tensor& xbc, int64_t col_b, int64_t col_c, const Tensor& dt_
   check(nrl_ssd_scan(f32(xbc, "xbc"), xbc.stride(0), static_cast<int>(col_b), static_cast<int>(col_c), f32(dt_raw, "dt_raw"),
                      dt_raw.stride(0), f32(dt_bias, "dt_bias"), f32(A_log, "A_log"), f32(Dskip, "D"), f32w(state, "state"), f32w(y, "y"),
                      i32(cu, "cu"), i32(start, "start"), i32(state_slot, "state_slot"), E, heads, static_cast<int>(groups), N, P,
-                     cur_stream()),
+                     static_cast<int>(impl), cur_stream()),
         "ssd_scan");
 }
 
@@ -131,7 +132,7 @@ void delta_prep(Tensor qkv, int64_t col_k, const Tensor& b_raw, const Tensor& a_
 }
 
 void delta_scan(const Tensor& qkv, int64_t col_k, int64_t col_v, const Tensor& beta, const Tensor& decay, Tensor state, Tensor o,
-                const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t kv_heads, bool per_channel) {
+                const Tensor& cu, const Tensor& start, const Tensor& state_slot, int64_t kv_heads, bool per_channel, int64_t impl) {
   c10::cuda::CUDAGuard guard(o.device());
   TORCH_CHECK(state.dim() == 4 && state.is_contiguous(), "delta_scan: state [slots, heads, D, Dv]");
   const int heads = static_cast<int>(state.size(1)), D = static_cast<int>(state.size(2)), Dv = static_cast<int>(state.size(3));
@@ -139,7 +140,8 @@ void delta_scan(const Tensor& qkv, int64_t col_k, int64_t col_v, const Tensor& b
   TORCH_CHECK(qkv.dim() == 2 && col_v + heads * Dv <= qkv.size(1) && o.is_contiguous() && o.size(-1) == heads * Dv, "delta_scan: shapes");
   check(nrl_delta_scan(f32(qkv, "qkv"), qkv.stride(0), static_cast<int>(col_k), static_cast<int>(col_v), f32(beta, "beta"),
                        f32(decay, "decay"), f32w(state, "state"), f32w(o, "o"), i32(cu, "cu"), i32(start, "start"),
-                       i32(state_slot, "state_slot"), E, heads, static_cast<int>(kv_heads), D, Dv, per_channel ? 1 : 0, cur_stream()),
+                       i32(state_slot, "state_slot"), E, heads, static_cast<int>(kv_heads), D, Dv, per_channel ? 1 : 0,
+                       static_cast<int>(impl), cur_stream()),
         "delta_scan");
 }
 
@@ -162,7 +164,7 @@ void qknorm_kv_write(Tensor q, const Tensor& k, const Tensor& v, const Tensor& q
 }
 
 void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table, const Tensor& tok_entry,
-                      const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out) {
+                      const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out, int64_t impl) {
   const bool single_token = block_table.size(0) == q.size(0);
   c10::cuda::CUDAGuard guard(q.device());
   const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
@@ -173,7 +175,8 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   check(nrl_window_attention(f32(q, "q"), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
                              i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
                              i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
-                             out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, cur_stream()),
+                             out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
+                             cur_stream()),
         "window_attention");
 }
 
@@ -190,6 +193,8 @@ void bind_hybrid(pybind11::module_& m) {
   m.def("delta_prep", &delta_prep, "unit q / k, beta and decays of the gated delta rule");
   m.def("delta_scan", &delta_scan, "gated delta rule scan, state carried per slot");
   m.def("qknorm_kv_write", &qknorm_kv_write, "per-head RMS norm of q (in place) and k (into the paged cache), v into the cache");
-  m.def("window_attention", &window_attention, "sliding-window attention over the paged cache");
+  m.def("window_attention", &window_attention, "sliding-window attention over the paged cache", pybind11::arg("q"),
+        pybind11::arg("k_cache"), pybind11::arg("v_cache"), pybind11::arg("block_table"), pybind11::arg("tok_entry"), pybind11::arg("pos"),
+        pybind11::arg("window"), pybind11::arg("scale"), pybind11::arg("out_scale"), pybind11::arg("out"), pybind11::arg("impl") = 0);
 }
 }  // namespace nrl

@@ -47,7 +47,9 @@ cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const 
 //   dt = softplus(dt_raw + dt_bias);  S = exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x      -> y float [T, heads*P]
 cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const float* dt_raw, long sd, const float* dt_bias,
                          const float* A_log, const float* Dskip, float* state, float* y, const int* cu, const int* start,
-                         const int* state_slot, int E, int heads, int groups, int N, int P, cudaStream_t s);
+                         const int* state_slot, int E, int heads, int groups, int N, int P, int impl, cudaStream_t s);
+// `impl` of both scans: 0 picks by size; 1 a state column per thread (rows <= 128); 2 row groups of a column per thread;
+// 3 the state in shared memory.  A kernel that does not fit the sizes returns cudaErrorInvalidValue.
 
 // Gated delta rule inputs.  qkv float [T, *] (row stride sq): q at column 0, k at col_k (kv_heads*D each); both are made unit
 // vectors per head in place (x / sqrt(sum x^2 + 1e-6)), q also times D^-1/2.  beta = sigmoid(b_raw).
@@ -60,7 +62,7 @@ cudaError_t nrl_delta_prep(float* qkv, long sq, int col_k, const float* b_raw, l
 // state float [slots, heads, D, Dv];  o float [T, heads*Dv].
 cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, const float* beta, const float* decay, float* state,
                            float* o, const int* cu, const int* start, const int* state_slot, int E, int heads, int kv_heads, int D,
-                           int Dv, int per_channel, cudaStream_t s);
+                           int Dv, int per_channel, int impl, cudaStream_t s);
 
 // Per-head RMS norm (weight [D], shared by heads) of q in place and of k into the paged cache; v into the paged cache.
 // q float [T, Hq*D] (row stride sq), k float [T, Hkv*D], v float [T, Hkv*Dv] (row strides sk, sv).
@@ -74,5 +76,14 @@ cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, cons
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D,
-                                 int Dv, int page, int single_token, cudaStream_t s);
+                                 int Dv, int page, int single_token, int impl, cudaStream_t s);
+// `impl`: 0 picks by shape and step kind, 1 the scalar tile kernel, 2 one block per (token, head), 3 the tensor-core kernel.
+
+// Tensor-core kernel for prompt portions over bf16 pages of 16 tokens (attention_window_mma.cu); `_fits` says whether the
+// shapes and the output's alignment allow it.
+int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int D, int Dv, int page);
+cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
+                                     int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
+                                     void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
+                                     cudaStream_t s);
 }

@@ -410,6 +410,189 @@ delta_scan_reg_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Column-resident scans (state rows <= 128, the usual sizes): thread c keeps the whole column c of the state in ROWS
+// registers, so S^T k, S^T q and S^T C are sums inside one thread -- no reduction across threads -- and a token costs one
+// barrier: the vectors all columns share (B and C, or q, k and the row decays) are staged in shared memory, double
+// buffered, zero padded to ROWS, and fetched from global memory one token ahead.
+// ---------------------------------------------------------------------------------------------------------------------
+__host__ __device__ constexpr int col_min_threads(int rows) { return rows > 64 ? 64 : 32; }      // so that a thread stages few values per token
+
+template <int ROWS>
+__global__ void __launch_bounds__(256)
+ssd_scan_col_kernel(const float* __restrict__ xbc, long sx, int col_b, int col_c, const float* __restrict__ dt_raw, long sd,
+                    const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                    float* __restrict__ state, float* __restrict__ y, const int* __restrict__ cu, const int* __restrict__ start,
+                    const int* __restrict__ state_slot, int heads, int groups, int N, int P) {
+  constexpr int L = 2 * ROWS + 4;                // per token: B | C | dt, decay
+  constexpr int kStagePre = (2 * ROWS + col_min_threads(ROWS) - 1) / col_min_threads(ROWS);
+  __shared__ __align__(16) float stage[2 * L];
+  const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / groups);
+  const int tid = threadIdx.x, nth = blockDim.x, p = tid;
+  const bool live = p < P;
+  float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * N * P;
+  const bool carried = start[e] > 0;
+  float S[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) S[i] = (live && i < N && carried) ? gS[static_cast<long>(i) * P + p] : 0.f;
+  const float negA = -expf(A_log[h]), dskip = Dskip[h], bias = dt_bias[h];
+  const int t0 = cu[e], t1 = cu[e + 1];
+  float pre[kStagePre], pre_x, pre_dt;
+  auto fetch = [&](int t) {
+    const float* row = xbc + static_cast<long>(t) * sx;
+#pragma unroll
+    for (int i = 0; i < kStagePre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < 2 * ROWS) {
+        const int n = idx < ROWS ? idx : idx - ROWS;
+        pre[i] = n < N ? row[(idx < ROWS ? col_b : col_c) + g * N + n] : 0.f;
+      }
+    }
+    pre_x = live ? row[h * P + p] : 0.f;
+    pre_dt = dt_raw[static_cast<long>(t) * sd + h];
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float* v = stage + ((t - t0) & 1) * L;
+#pragma unroll
+    for (int i = 0; i < kStagePre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < 2 * ROWS) v[idx] = pre[i];
+    }
+    if (tid == 0) {
+      const float dt = softplus(pre_dt + bias);
+      v[2 * ROWS] = dt;
+      v[2 * ROWS + 1] = expf(negA * dt);
+    }
+    const float x_cur = pre_x;
+    __syncthreads();
+    if (t + 1 < t1) fetch(t + 1);
+    const float dt = v[2 * ROWS], a = v[2 * ROWS + 1];
+    const float xs = dt * x_cur;
+    const float4* vB = reinterpret_cast<const float4*>(v);
+    const float4* vC = reinterpret_cast<const float4*>(v + ROWS);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < ROWS / 4; ++i) {
+      const float4 b = vB[i], c = vC[i];
+      S[4 * i] = a * S[4 * i] + b.x * xs;
+      S[4 * i + 1] = a * S[4 * i + 1] + b.y * xs;
+      S[4 * i + 2] = a * S[4 * i + 2] + b.z * xs;
+      S[4 * i + 3] = a * S[4 * i + 3] + b.w * xs;
+      acc[0] += S[4 * i] * c.x;
+      acc[1] += S[4 * i + 1] * c.y;
+      acc[2] += S[4 * i + 2] * c.z;
+      acc[3] += S[4 * i + 3] * c.w;
+    }
+    if (live) y[static_cast<long>(t) * heads * P + h * P + p] = (acc[0] + acc[1]) + (acc[2] + acc[3]) + dskip * x_cur;
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+      if (i < N) gS[static_cast<long>(i) * P + p] = S[i];
+  }
+}
+
+template <int ROWS>
+__global__ void __launch_bounds__(256)
+delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col_v, const float* __restrict__ beta,
+                      const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o, const int* __restrict__ cu,
+                      const int* __restrict__ start, const int* __restrict__ state_slot, int heads, int kv_heads, int D, int Dv,
+                      int per_channel) {
+  constexpr int L = 3 * ROWS + 4;                // per token: q | k | row decays | beta
+  constexpr int kStagePre = (3 * ROWS + col_min_threads(ROWS) - 1) / col_min_threads(ROWS);
+  __shared__ __align__(16) float stage[2 * L];
+  const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / kv_heads);
+  const int tid = threadIdx.x, nth = blockDim.x, c = tid;
+  const bool live = c < Dv;
+  float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * D * Dv;
+  const bool carried = start[e] > 0;
+  float S[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) S[i] = (live && i < D && carried) ? gS[static_cast<long>(i) * Dv + c] : 0.f;
+  const int t0 = cu[e], t1 = cu[e + 1];
+  const int nd = per_channel ? heads * D : heads;
+  float pre[kStagePre], pre_v, pre_beta;
+  auto fetch = [&](int t) {
+    const float* row = qkv + static_cast<long>(t) * sq;
+#pragma unroll
+    for (int i = 0; i < kStagePre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < 3 * ROWS) {
+        const int part = idx / ROWS, d = idx - part * ROWS;
+        float x = 0.f;
+        if (d < D) {
+          if (part == 0) x = row[g * D + d];
+          else if (part == 1) x = row[col_k + g * D + d];
+          else x = decay[static_cast<long>(t) * nd + (per_channel ? h * D + d : h)];
+        }
+        pre[i] = x;
+      }
+    }
+    pre_v = live ? row[col_v + h * Dv + c] : 0.f;
+    pre_beta = beta[static_cast<long>(t) * heads + h];
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float* v = stage + ((t - t0) & 1) * L;
+#pragma unroll
+    for (int i = 0; i < kStagePre; ++i) {
+      const int idx = tid + i * nth;
+      if (idx < 3 * ROWS) v[idx] = pre[i];
+    }
+    const float v_cur = pre_v, b_cur = pre_beta;
+    __syncthreads();
+    if (t + 1 < t1) fetch(t + 1);
+    const float4* vq = reinterpret_cast<const float4*>(v);
+    const float4* vk = reinterpret_cast<const float4*>(v + ROWS);
+    const float4* vg = reinterpret_cast<const float4*>(v + 2 * ROWS);
+    float pk[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < ROWS / 4; ++i) {                       // S <- g S;  S^T k
+      const float4 gg = vg[i], kk = vk[i];
+      S[4 * i] *= gg.x;
+      S[4 * i + 1] *= gg.y;
+      S[4 * i + 2] *= gg.z;
+      S[4 * i + 3] *= gg.w;
+      pk[0] += S[4 * i] * kk.x;
+      pk[1] += S[4 * i + 1] * kk.y;
+      pk[2] += S[4 * i + 2] * kk.z;
+      pk[3] += S[4 * i + 3] * kk.w;
+    }
+    const float u = b_cur * (v_cur - ((pk[0] + pk[1]) + (pk[2] + pk[3])));
+    float po[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < ROWS / 4; ++i) {                       // S <- S + k u^T;  o = S^T q sees this token's write
+      const float4 kk = vk[i], qq = vq[i];
+      S[4 * i] += kk.x * u;
+      S[4 * i + 1] += kk.y * u;
+      S[4 * i + 2] += kk.z * u;
+      S[4 * i + 3] += kk.w * u;
+      po[0] += S[4 * i] * qq.x;
+      po[1] += S[4 * i + 1] * qq.y;
+      po[2] += S[4 * i + 2] * qq.z;
+      po[3] += S[4 * i + 3] * qq.w;
+    }
+    if (live) o[static_cast<long>(t) * heads * Dv + h * Dv + c] = (po[0] + po[1]) + (po[2] + po[3]);
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+      if (i < D) gS[static_cast<long>(i) * Dv + c] = S[i];
+  }
+}
+
+// template size and block size of the column-resident kernels for a state of `rows` x `cols`; false when they do not fit
+bool pick_col_layout(int cols, int rows, int* rows_t, int* threads_out) {
+  if (rows > 128 || cols < 1 || cols > 256) return false;
+  const int rt = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  int threads = ((cols + 31) / 32) * 32;
+  if (threads < col_min_threads(rt)) threads = col_min_threads(rt);
+  *rows_t = rt;
+  *threads_out = threads;
+  return true;
+}
+
 // rows per thread / row groups for a state of `rows` x `cols`: as many row groups as 512 threads allow (256 when a thread
 // holds 64 rows), at most 64 rows per thread, and enough threads to fetch a token's inputs with kPre loads each
 bool pick_reg_layout(int cols, int rows, int per_token, int* R_out, int* rpt_out, int* threads_out) {
@@ -470,10 +653,24 @@ cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const 
 
 cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const float* dt_raw, long sd, const float* dt_bias,
                          const float* A_log, const float* Dskip, float* state, float* y, const int* cu, const int* start,
-                         const int* state_slot, int E, int heads, int groups, int N, int P, cudaStream_t s) {
+                         const int* state_slot, int E, int heads, int groups, int N, int P, int impl, cudaStream_t s) {
   if (E <= 0) return cudaSuccess;
-  if (P > 512 || heads % groups != 0) return cudaErrorInvalidValue;
-  {
+  if (P > 512 || heads % groups != 0 || impl < 0 || impl > 3) return cudaErrorInvalidValue;
+  if (impl == 0 || impl == 1) {
+    int rt, threads;
+    if (pick_col_layout(P, N, &rt, &threads)) {
+#define NRL_SSDC(R_)                                                                                                               \
+  if (rt == R_) {                                                                                                                  \
+    ssd_scan_col_kernel<R_><<<dim3(E, heads), threads, 0, s>>>(xbc, sx, col_b, col_c, dt_raw, sd, dt_bias, A_log, Dskip, state, y, cu, \
+                                                               start, state_slot, heads, groups, N, P);                            \
+    return cudaGetLastError();                                                                                                     \
+  }
+      NRL_SSDC(16) NRL_SSDC(32) NRL_SSDC(64) NRL_SSDC(128)
+#undef NRL_SSDC
+    }
+    if (impl == 1) return cudaErrorInvalidValue;
+  }
+  if (impl != 3) {
     int R, rpt, threads;
     const size_t smem_reg = sizeof(float) * (2 * (2 * static_cast<size_t>(N) + P) + 512);
     if (pick_reg_layout(P, N, 2 * N + P, &R, &rpt, &threads) && smem_reg <= 48 * 1024) {
@@ -487,6 +684,7 @@ cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const 
       NRL_SSD(4) NRL_SSD(8) NRL_SSD(16) NRL_SSD(32) NRL_SSD(64)
 #undef NRL_SSD
     }
+    if (impl == 2) return cudaErrorInvalidValue;
   }
   const int R = pick_rows(P, N);
   const int threads = ((P * R + 31) / 32) * 32;
@@ -514,10 +712,24 @@ cudaError_t nrl_delta_prep(float* qkv, long sq, int col_k, const float* b_raw, l
 
 cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, const float* beta, const float* decay, float* state,
                            float* o, const int* cu, const int* start, const int* state_slot, int E, int heads, int kv_heads, int D,
-                           int Dv, int per_channel, cudaStream_t s) {
+                           int Dv, int per_channel, int impl, cudaStream_t s) {
   if (E <= 0) return cudaSuccess;
-  if (Dv > 512 || heads % kv_heads != 0) return cudaErrorInvalidValue;
-  {
+  if (Dv > 512 || heads % kv_heads != 0 || impl < 0 || impl > 3) return cudaErrorInvalidValue;
+  if (impl == 0 || impl == 1) {
+    int rt, threads;
+    if (pick_col_layout(Dv, D, &rt, &threads)) {
+#define NRL_DELTAC(R_)                                                                                                             \
+  if (rt == R_) {                                                                                                                  \
+    delta_scan_col_kernel<R_><<<dim3(E, heads), threads, 0, s>>>(qkv, sq, col_k, col_v, beta, decay, state, o, cu, start, state_slot,  \
+                                                                 heads, kv_heads, D, Dv, per_channel);                             \
+    return cudaGetLastError();                                                                                                     \
+  }
+      NRL_DELTAC(16) NRL_DELTAC(32) NRL_DELTAC(64) NRL_DELTAC(128)
+#undef NRL_DELTAC
+    }
+    if (impl == 1) return cudaErrorInvalidValue;
+  }
+  if (impl != 3) {
     int R, rpt, threads;
     const size_t smem_reg = sizeof(float) * (6 * static_cast<size_t>(D) + 2 * 512 + 64);
     if (pick_reg_layout(Dv, D, 3 * D, &R, &rpt, &threads) && smem_reg <= 48 * 1024) {
@@ -531,6 +743,7 @@ cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, cons
       NRL_DELTA(4) NRL_DELTA(8) NRL_DELTA(16) NRL_DELTA(32) NRL_DELTA(64)
 #undef NRL_DELTA
     }
+    if (impl == 2) return cudaErrorInvalidValue;
   }
   const int R = pick_rows(Dv, D);
   const int threads = ((Dv * R + 31) / 32) * 32;

@@ -41,9 +41,13 @@ def causal_conv(x, w, bias, state, out, plan):
     _ext().causal_conv(x, w, bias, state, out, plan.cu, plan.tok_entry, plan.start, plan.state_slot)
 
 
-def ssd_scan(xbc, col_b, col_c, dt_raw, dt_bias, A_log, D, state, y, plan, groups):
+SCAN_IMPLS = {"auto": 0, "column": 1, "rows": 2, "shared": 3}
+
+
+def ssd_scan(xbc, col_b, col_c, dt_raw, dt_bias, A_log, D, state, y, plan, groups, impl: str = "auto"):
     native._count()
-    _ext().ssd_scan(xbc, col_b, col_c, dt_raw, dt_bias, A_log, D, state, y, plan.cu, plan.start, plan.state_slot, groups)
+    _ext().ssd_scan(xbc, col_b, col_c, dt_raw, dt_bias, A_log, D, state, y, plan.cu, plan.start, plan.state_slot, groups,
+                    SCAN_IMPLS[impl])
 
 
 def delta_prep(qkv, col_k, b_raw, a_raw, dt_bias, A_log, beta, decay, kv_heads, dim, per_channel):
@@ -51,9 +55,10 @@ def delta_prep(qkv, col_k, b_raw, a_raw, dt_bias, A_log, beta, decay, kv_heads, 
     _ext().delta_prep(qkv, col_k, b_raw, a_raw, dt_bias, A_log, beta, decay, kv_heads, dim, per_channel)
 
 
-def delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan, kv_heads, per_channel):
+def delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan, kv_heads, per_channel, impl: str = "auto"):
     native._count()
-    _ext().delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan.cu, plan.start, plan.state_slot, kv_heads, per_channel)
+    _ext().delta_scan(qkv, col_k, col_v, beta, decay, state, o, plan.cu, plan.start, plan.state_slot, kv_heads, per_channel,
+                      SCAN_IMPLS[impl])
 
 
 def qknorm_kv_write(q, k, v, qw, kw, eps, k_cache, v_cache, plan):
@@ -61,6 +66,12 @@ def qknorm_kv_write(q, k, v, qw, kw, eps, k_cache, v_cache, plan):
     _ext().qknorm_kv_write(q, k, v, qw, kw, eps, k_cache, v_cache, plan.kv_slot)
 
 
-def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out):
+WINDOW_IMPLS = {"auto": 0, "tile": 1, "simple": 2, "mma": 3}
+
+
+def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out, impl: str = "auto"):
+    """``impl``: "auto" (tensor cores for prompt portions over bf16 pages, the scalar tile kernel otherwise) or one kernel by
+    name; a kernel that does not fit the shapes raises."""
     native._count()
-    _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out)
+    _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out,
+                            WINDOW_IMPLS[impl])
