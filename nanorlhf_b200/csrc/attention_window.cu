@@ -367,14 +367,13 @@ cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, cons
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D, int Dv,
-                                 int page, int single_token, int impl, cudaStream_t s) {
+                                 int page, int single_token, int impl, int nsplit, float* part, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
   if (Dv > 32 * kMaxDvPerLane || Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
   // prompt portions over bf16 pages: tensor cores
-  if ((impl == 0 || impl == 3) && !cache_f32 && (!single_token || impl == 3) &&
-      nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page))
+  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page))
     return nrl_window_attention_mma(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so,
-                                    T, Hq, Hkv, D, Dv, page, single_token, s);
+                                    T, Hq, Hkv, D, Dv, page, single_token, single_token ? nsplit : 1, part, s);
   if (impl == 3) return cudaErrorInvalidValue;
   if (impl != 2 && Dv <= 128 && Dv % 4 == 0 && D <= 512) {
     // queries per block: the heads of one key/value head for single-token steps, 16 (tokens x heads) when entries hold runs

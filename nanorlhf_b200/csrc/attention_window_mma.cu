@@ -77,14 +77,17 @@ __global__ void __launch_bounds__(kThreads)
 window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
                             const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                             const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale, float out_scale,
-                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT) {
+                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT,
+                            int nsplit, float* __restrict__ part) {
   constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kBM][LDK]
   __nv_bfloat16* sK = sQ + kBM * LDK;                                         // [2][kBN][LDK]
   __nv_bfloat16* sV = sK + 2 * kBN * LDK;                                     // [2][kBN][LDV]
-  const int g = blockIdx.y, per_g = Hq / Hkv, h0 = g * per_g + blockIdx.z * HB;
-  const int hb = min(HB, per_g - static_cast<int>(blockIdx.z) * HB);
+  // nsplit > 1 (steps of single tokens, all heads of the group in one block): blockIdx.z = which part of the key walk
+  const int zb = nsplit > 1 ? 0 : static_cast<int>(blockIdx.z), split = nsplit > 1 ? static_cast<int>(blockIdx.z) : 0;
+  const int g = blockIdx.y, per_g = Hq / Hkv, h0 = g * per_g + zb * HB;
+  const int hb = min(HB, per_g - zb * HB);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   const int t_begin = blockIdx.x * QT, t_end = min(T, t_begin + QT);
 
@@ -145,13 +148,17 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     const bool warp_full = wt_lo >= t && wt_hi < tn;       // every row of the warp that holds a query belongs to this run
     const int whi = p_first + (wb - t), wlo = p_first + (wa - t) - window + 1;
 
+    const int per_split = (nblk + nsplit - 1) / nsplit;
+    const int ib0 = split * per_split, ib1 = min(nblk, ib0 + per_split);
     __syncthreads();                                       // the previous run's last block has been consumed
-    load_kv_block(sK, k_cache, bt, Hkv, g, kb0, hi, D, DP);
-    load_kv_block(sV, v_cache, bt, Hkv, g, kb0, hi, Dv, DVP);
-    cp_commit();
-    for (int ib = 0; ib < nblk; ++ib) {
-      const int kb = kb0 + ib * kBN, buf = ib & 1;
-      if (ib + 1 < nblk) {
+    if (ib0 < ib1) {
+      load_kv_block(sK, k_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, D, DP);
+      load_kv_block(sV, v_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, Dv, DVP);
+      cp_commit();
+    }
+    for (int ib = ib0; ib < ib1; ++ib) {
+      const int kb = kb0 + ib * kBN, buf = (ib - ib0) & 1;
+      if (ib + 1 < ib1) {
         load_kv_block(sK + (buf ^ 1) * kBN * LDK, k_cache, bt, Hkv, g, kb + kBN, hi, D, DP);
         load_kv_block(sV + (buf ^ 1) * kBN * LDV, v_cache, bt, Hkv, g, kb + kBN, hi, Dv, DVP);
         cp_commit();
@@ -254,7 +261,7 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     }
     t = tn;
   }
-  // ---- out = out_scale * O / l ----
+  // ---- out = out_scale * O / l, or this part's (O, max, l) for the merge ----
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     float l = l_run[hf];
@@ -262,6 +269,22 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     if (!row_ok[hf]) continue;
     const int r = w * 16 + gq + hf * 8;
+    if (nsplit > 1) {
+      float* pd = part + ((static_cast<long>(row_t[hf]) * Hq + h0 + r % HB) * nsplit + split) * (Dv + 2);
+#pragma unroll
+      for (int i = 0; i < 2 * NV; ++i) {
+        const int c = i * 8 + 2 * tq;
+        if (c < Dv) {
+          pd[c] = o[i][2 * hf];
+          pd[c + 1] = o[i][2 * hf + 1];
+        }
+      }
+      if (tq == 0) {
+        pd[Dv] = m_run[hf];
+        pd[Dv + 1] = l;
+      }
+      continue;
+    }
     __nv_bfloat16* dst = out + static_cast<long>(row_t[hf]) * so + static_cast<long>(h0 + r % HB) * Dv;
     const float f = out_scale / l;
 #pragma unroll
@@ -272,10 +295,33 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
   }
 }
 
+// block per (token, query head): out = out_scale * sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s
+__global__ void window_attention_merge_kernel(const float* __restrict__ part, int nsplit, int Hq, int Dv, float out_scale,
+                                              __nv_bfloat16* __restrict__ out, long so) {
+  const long t = blockIdx.x;
+  const int h = blockIdx.y;
+  const float* p = part + (t * Hq + h) * nsplit * (Dv + 2);
+  float M = -INFINITY;
+  for (int x = 0; x < nsplit; ++x) M = fmaxf(M, p[x * (Dv + 2) + Dv]);
+  float L = 0.f;
+  for (int x = 0; x < nsplit; ++x) {
+    const float m = p[x * (Dv + 2) + Dv];
+    if (m != -INFINITY) L += ex2(m - M) * p[x * (Dv + 2) + Dv + 1];
+  }
+  for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+    float a = 0.f;
+    for (int x = 0; x < nsplit; ++x) {
+      const float m = p[x * (Dv + 2) + Dv];
+      if (m != -INFINITY) a += ex2(m - M) * p[x * (Dv + 2) + c];
+    }
+    out[t * so + static_cast<long>(h) * Dv + c] = __float2bfloat16_rn(out_scale * (a / L));
+  }
+}
+
 template <int KS, int NV>
 cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                    const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T, int Hq,
-                   int Hkv, int D, int Dv, int single_token, cudaStream_t s) {
+                   int Hkv, int D, int Dv, int single_token, int nsplit, float* part, cudaStream_t s) {
   const int per_g = Hq / Hkv;
   // a step of single tokens: one token per block (every token walks its own sequence; more blocks, shorter walks)
   const int HB = per_g < kBM ? per_g : kBM, QT = single_token ? 1 : kBM / HB;
@@ -288,16 +334,33 @@ cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_c
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const dim3 grid((T + QT - 1) / QT, Hkv, (per_g + HB - 1) / HB);
+  if (nsplit > 1 && (!single_token || per_g > kBM || part == nullptr)) return cudaErrorInvalidValue;
+  const dim3 grid((T + QT - 1) / QT, Hkv, nsplit > 1 ? nsplit : (per_g + HB - 1) / HB);
   kern<<<grid, kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
                                     block_table, max_blocks, tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so,
-                                    T, Hq, Hkv, D, Dv, HB, QT);
+                                    T, Hq, Hkv, D, Dv, HB, QT, nsplit, part);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || nsplit <= 1) return e;
+  window_attention_merge_kernel<<<dim3(T, Hq), Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128, 0, s>>>(part, nsplit, Hq, Dv, out_scale,
+                                                                                          static_cast<__nv_bfloat16*>(out), so);
   return cudaGetLastError();
 }
 
 }  // namespace
 
 extern "C" {
+
+// In how many parts a step of single tokens walks its keys so that the grid fills the GPU (1: no parts, no merge).
+int nrl_window_attention_splits(int T, int Hq, int Hkv, int window, int max_blocks, int page) {
+  if (Hkv <= 0 || Hq / Hkv > kBM) return 1;
+  const long keys = static_cast<long>(max_blocks) * page < window ? static_cast<long>(max_blocks) * page : window;
+  const int nblk = static_cast<int>((keys + kBN - 1) / kBN) + 1;
+  const long blocks = static_cast<long>(T) * Hkv;
+  long want = (2 * 148 + blocks - 1) / blocks;
+  if (want > nblk) want = nblk;
+  if (want > 16) want = 16;
+  return want < 1 ? 1 : static_cast<int>(want);
+}
 
 int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int D, int Dv, int page) {
   return page == 16 && Hkv > 0 && Hq % Hkv == 0 && D % 8 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && so % 2 == 0 &&
@@ -307,14 +370,14 @@ int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int
 cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
-                                     cudaStream_t s) {
+                                     int nsplit, float* part, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
   if (!nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) || window < 1) return cudaErrorInvalidValue;
   const int ks = D <= 32 ? 2 : D <= 64 ? 4 : 8, nv = Dv <= 32 ? 2 : Dv <= 64 ? 4 : 8;
 #define NRL_WM(KS_, NV_)                                                                                                         \
   if (ks == KS_ && nv == NV_)                                                                                                    \
     return launch<KS_, NV_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so, T, Hq, \
-                            Hkv, D, Dv, single_token, s);
+                            Hkv, D, Dv, single_token, nsplit, part, s);
   NRL_WM(2, 2) NRL_WM(2, 4) NRL_WM(2, 8) NRL_WM(4, 2) NRL_WM(4, 4) NRL_WM(4, 8) NRL_WM(8, 2) NRL_WM(8, 4) NRL_WM(8, 8)
 #undef NRL_WM
   return cudaErrorInvalidValue;

@@ -275,7 +275,8 @@ def test_needle_just_inside_and_outside_the_window(tmp_path, window, dtype):
 
 @pytest.mark.parametrize("D,Dv,Hq,Hkv,window", [(128, 128, 8, 2, 100), (24, 16, 6, 3, 11), (64, 32, 4, 4, 40), (40, 72, 3, 1, 33),
                                                 (16, 16, 5, 1, 17), (32, 128, 2, 1, 64)])
-def test_window_attention_kernels_against_plain_softmax(D, Dv, Hq, Hkv, window):
+@pytest.mark.parametrize("step", ["portions", "single_tokens"])
+def test_window_attention_kernels_against_plain_softmax(D, Dv, Hq, Hkv, window, step):
     """Every window-attention kernel on random bf16 pages, entries of unequal length with and without earlier context, against
     a masked softmax written out per query.  Scores are made peaky so that one wrongly seen or missed key shows."""
     from nanorlhf_b200 import _C
@@ -285,6 +286,8 @@ def test_window_attention_kernels_against_plain_softmax(D, Dv, Hq, Hkv, window):
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(D * 1000 + window)
     old, new = [0, 37, 130, 5, 64, 200], [70, 1, 33, 2, 1, 17]
+    if step == "single_tokens":                                  # a decode step: the key walk is cut into parts and merged
+        old, new = [1, 37, 130, 15, 64, 200], [1] * 6
     sched = _C.StepScheduler(64, 16, len(old))
     sids = [sched.open() for _ in old]
     sched.plan([s for s, n in zip(sids, old) if n], [n for n in old if n])
