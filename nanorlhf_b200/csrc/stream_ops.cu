@@ -118,6 +118,38 @@ __global__ void gated_part_rmsnorm_kernel(const float* __restrict__ y, long sy, 
   }
 }
 
+// one block per (token, part): wide parts (a warp alone would walk them serially)
+template <typename OT>
+__global__ void gated_part_rmsnorm_block_kernel(const float* __restrict__ y, long sy, const float* __restrict__ gate, long sg,
+                                                const float* __restrict__ w, int shared_w, int part, int gate_act, int gate_first,
+                                                float eps, float scale, OT* __restrict__ out, long so, int nparts) {
+  __shared__ float red[8];
+  const long t = blockIdx.x / nparts;
+  const int p = static_cast<int>(blockIdx.x - t * nparts);
+  const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* yr = y + t * sy + static_cast<long>(p) * part;
+  const float* gr = gate + t * sg + static_cast<long>(p) * part;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < part; c += blockDim.x) {
+    float v = yr[c];
+    if (gate_first) v *= gate_fn(gr[c], gate_act);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[wi] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < nw; ++i) tot += red[i];
+  const float r = 1.f / sqrtf(tot / static_cast<float>(part) + eps);
+  for (int c = threadIdx.x; c < part; c += blockDim.x) {
+    float v = yr[c];
+    const float gv = gate_fn(gr[c], gate_act);
+    const float wv = w[shared_w ? c : p * part + c];
+    v = gate_first ? (v * gv) * r * wv : v * r * wv * gv;
+    st(out, t * so + static_cast<long>(p) * part + c, scale * v);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -164,6 +196,16 @@ cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, l
   if (part <= 0 || n % part != 0) return cudaErrorInvalidValue;
   const int nparts = n / part;
   const long warps = static_cast<long>(T) * nparts;
+  if (part >= 256) {
+    const int th = part >= 512 ? 256 : 128;
+    if (out_f32)
+      gated_part_rmsnorm_block_kernel<float><<<static_cast<unsigned>(warps), th, 0, s>>>(
+          y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale, static_cast<float*>(out), so, nparts);
+    else
+      gated_part_rmsnorm_block_kernel<__nv_bfloat16><<<static_cast<unsigned>(warps), th, 0, s>>>(
+          y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale, static_cast<__nv_bfloat16*>(out), so, nparts);
+    return cudaGetLastError();
+  }
   const int blocks = static_cast<int>((warps + 3) / 4);
   if (out_f32)
     gated_part_rmsnorm_kernel<float><<<blocks, 128, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale,

@@ -320,6 +320,24 @@ def test_window_attention_kernels_against_plain_softmax(D, Dv, Hq, Hkv, window, 
         assert err < 2e-2, (impl, err)
 
 
+@pytest.mark.parametrize("part,nparts", [(12, 5), (64, 2), (256, 3), (300, 1), (1024, 2)])
+@pytest.mark.parametrize("gate_act,gate_first", [("silu", True), ("sigmoid", False)])
+def test_gated_part_rmsnorm_narrow_and_wide_parts(part, nparts, gate_act, gate_first):
+    from nanorlhf_b200.ops import hybrid as hy, native
+    native.load()
+    g = torch.Generator().manual_seed(part)
+    T, n = 9, part * nparts
+    y, gate, w = torch.randn(T, n, generator=g), torch.randn(T, n, generator=g), torch.rand(n, generator=g) + 0.5
+    act = (lambda z: z * torch.sigmoid(z)) if gate_act == "silu" else torch.sigmoid
+    yd, gd = y.double().view(T, nparts, part), act(gate.double()).view(T, nparts, part)
+    v = yd * gd if gate_first else yd
+    v = v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5) * w.double().view(nparts, part)
+    want = 0.6 * (v if gate_first else v * gd).view(T, n)
+    out = torch.empty(T, n, device="cuda")
+    hy.gated_part_rmsnorm(y.cuda(), gate.cuda(), w.cuda(), part, gate_act, gate_first, 1e-5, 0.6, out)
+    assert (out.double().cpu() - want).abs().max() < 1e-4
+
+
 def _scan_plan(old, new, dev):
     from nanorlhf_b200 import _C
     from nanorlhf_b200.sampler.hybrid_sampler import StepPlan
