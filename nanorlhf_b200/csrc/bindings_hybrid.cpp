@@ -92,7 +92,7 @@ void causal_conv(const Tensor& in, const Tensor& w, const c10::optional<Tensor>&
   if (bias.has_value()) TORCH_CHECK(bias->numel() == C, "causal_conv: bias");
   check(nrl_causal_conv(f32(in, "in"), in.stride(0), f32(w, "w"), bias.has_value() ? f32(*bias, "bias") : nullptr, f32(state, "state"),
                         f32w(out, "out"), out.stride(0), i32(cu, "cu"), i32(tok_entry, "tok_entry"), i32(start, "start"),
-                        i32(state_slot, "state_slot"), T, C, taps, cur_stream()),
+                        i32(state_slot, "state_slot"), T, E, C, taps, cur_stream()),
         "causal_conv");
   check(nrl_causal_conv_carry(f32(in, "in"), in.stride(0), f32w(state, "state"), i32(cu, "cu"), i32(start, "start"),
                               i32(state_slot, "state_slot"), E, C, taps, cur_stream()),

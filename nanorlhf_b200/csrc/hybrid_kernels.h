@@ -37,8 +37,8 @@ cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, l
 // bias float [C] or null, state float [slots, taps-1, C] (oldest first).  out float [T, C] (row stride so).
 // nrl_causal_conv reads the old state; nrl_causal_conv_carry (launched after it) stores the step's last taps-1 inputs.
 cudaError_t nrl_causal_conv(const float* in, long si, const float* w, const float* bias, const float* state, float* out, long so,
-                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int C, int taps,
-                            cudaStream_t s);
+                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int E, int C,
+                            int taps, cudaStream_t s);
 cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const int* cu, const int* start, const int* state_slot,
                                   int E, int C, int taps, cudaStream_t s);
 

@@ -44,6 +44,62 @@ __global__ void causal_conv_kernel(const float* __restrict__ in, long si, const 
   out[t * so + c] = silu(acc);
 }
 
+// thread per (channel, run of kConvTok consecutive tokens): the last taps-1 inputs slide through registers, so every input is
+// read once (plus the history at the start of a run or of a sequence) and the taps' weights once per run
+constexpr int kConvTok = 8;
+
+template <int MAXT>
+__global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, const float* __restrict__ w, const float* __restrict__ bias,
+                                       const float* __restrict__ state, float* __restrict__ out, long so, const int* __restrict__ cu,
+                                       const int* __restrict__ tok_entry, const int* __restrict__ start,
+                                       const int* __restrict__ state_slot, int T, int C, int taps) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int t_begin = blockIdx.y * kConvTok, t_end = min(T, t_begin + kConvTok);
+  float wv[MAXT], hist[MAXT];
+#pragma unroll
+  for (int j = 0; j < MAXT; ++j) {
+    wv[j] = j < taps ? w[static_cast<long>(c) * taps + j] : 0.f;
+    hist[j] = 0.f;
+  }
+  const float b = bias != nullptr ? bias[c] : 0.f;
+  int e_prev = -1;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int e = tok_entry[t];
+    if (e != e_prev) {                                   // first token of the run, or another sequence begins: fetch the history
+      const long first = cu[e];
+      const int local = static_cast<int>(t - first);
+      const bool carried = start[e] > 0;
+      const float* st = state + static_cast<long>(state_slot[e]) * (taps - 1) * C;
+#pragma unroll
+      for (int j = 0; j < MAXT - 1; ++j) {
+        if (j < taps - 1) {
+          const int src = local - (taps - 1 - j);
+          float x = 0.f;
+          if (src >= 0) x = in[(first + src) * si + c];
+          else if (carried) x = st[static_cast<long>(taps - 1 + src) * C + c];
+          hist[j] = x;
+        }
+      }
+      e_prev = e;
+    }
+    const float cur = in[static_cast<long>(t) * si + c];
+    float acc = b;
+#pragma unroll
+    for (int j = 0; j < MAXT - 1; ++j)
+      if (j < taps - 1) acc += wv[j] * hist[j];
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j)
+      if (j == taps - 1) acc += wv[j] * cur;
+    out[static_cast<long>(t) * so + c] = silu(acc);
+#pragma unroll
+    for (int j = 0; j < MAXT - 1; ++j) {
+      if (j < taps - 2) hist[j] = hist[j + 1];
+      else if (j == taps - 2) hist[j] = cur;
+    }
+  }
+}
+
 // thread per (entry, channel): the slot keeps the last taps-1 inputs of the sequence, oldest first
 __global__ void causal_conv_carry_kernel(const float* __restrict__ in, long si, float* __restrict__ state, const int* __restrict__ cu,
                                          const int* __restrict__ start, const int* __restrict__ state_slot, int E, int C, int taps) {
@@ -632,10 +688,18 @@ int pick_rows(int cols, int rows) {
 extern "C" {
 
 cudaError_t nrl_causal_conv(const float* in, long si, const float* w, const float* bias, const float* state, float* out, long so,
-                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int C, int taps,
-                            cudaStream_t s) {
+                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int E, int C,
+                            int taps, cudaStream_t s) {
   if (T <= 0 || C <= 0) return cudaSuccess;
   if (taps < 1 || taps > kMaxTaps) return cudaErrorInvalidValue;
+  if (T >= 2 * kConvTok && T >= 2 * E && (T + kConvTok - 1) / kConvTok <= 65535) {     // prompt portions: runs of tokens per thread
+    const dim3 grid((C + 127) / 128, (T + kConvTok - 1) / kConvTok);
+    if (taps <= 4)
+      causal_conv_run_kernel<4><<<grid, 128, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start, state_slot, T, C, taps);
+    else
+      causal_conv_run_kernel<kMaxTaps><<<grid, 128, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start, state_slot, T, C, taps);
+    return cudaGetLastError();
+  }
   const long n = static_cast<long>(T) * C;
   causal_conv_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start,
                                                                            state_slot, T, C, taps);

@@ -3,6 +3,8 @@
 // Compiled WITHOUT fast-math: the float32 serving mode must stay within float rounding of a plain evaluation.
 #include <cuda_bf16.h>
 
+#include <cstdint>
+
 #include "hybrid_kernels.h"
 
 namespace {
@@ -84,13 +86,57 @@ __global__ void act_cols_kernel(const float* __restrict__ in, long si, OT* __res
   }
 }
 
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 u;
+  u.x = *reinterpret_cast<const unsigned*>(&a);
+  u.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+// V consecutive floats (V = 1 or 4; 4 needs 16-byte alignment)
+template <int V>
+__device__ __forceinline__ void ldv(const float* p, float (&v)[V]) {
+  if constexpr (V == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  } else {
+    v[0] = p[0];
+  }
+}
+template <int V, typename OT>
+__device__ __forceinline__ void stv(OT* p, const float (&v)[V]) {
+  if constexpr (V == 4) st4(p, v);
+  else st(p, 0, v[0]);
+}
+
+// four columns per thread: 128-bit loads, 64- / 128-bit stores
+template <typename OT>
+__global__ void act_cols_vec4_kernel(const float* __restrict__ in, long si, OT* __restrict__ out, long so, int act, long T, int C4) {
+  const long n = T * C4;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = idx / C4;
+    const int c = static_cast<int>(idx - t * C4) * 4;
+    float v[4];
+    ldv<4>(in + t * si + c, v);
+    if (act == 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i] = fmaxf(v[i], 0.f);
+        v[i] = v[i] * v[i];
+      }
+    }
+    st4(out + t * so + c, v);
+  }
+}
+
 __device__ __forceinline__ float gate_fn(float z, int act) {
   const float sg = 1.f / (1.f + expf(-z));
   return act == 0 ? z * sg : sg;
 }
 
-// one warp per (token, part)
-template <typename OT>
+// one warp per (token, part); V columns per lane and pass
+template <typename OT, int V>
 __global__ void gated_part_rmsnorm_kernel(const float* __restrict__ y, long sy, const float* __restrict__ gate, long sg,
                                           const float* __restrict__ w, int shared_w, int part, int gate_act, int gate_first,
                                           float eps, float scale, OT* __restrict__ out, long so, long T, int nparts) {
@@ -102,24 +148,34 @@ __global__ void gated_part_rmsnorm_kernel(const float* __restrict__ y, long sy, 
   const float* yr = y + t * sy + static_cast<long>(p) * part;
   const float* gr = gate + t * sg + static_cast<long>(p) * part;
   float ss = 0.f;
-  for (int c = lane; c < part; c += 32) {
-    float v = yr[c];
-    if (gate_first) v *= gate_fn(gr[c], gate_act);
-    ss += v * v;
+  for (int c = lane * V; c < part; c += 32 * V) {
+    float v[V], gv[V];
+    ldv<V>(yr + c, v);
+    if (gate_first) ldv<V>(gr + c, gv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      if (gate_first) v[i] *= gate_fn(gv[i], gate_act);
+      ss += v[i] * v[i];
+    }
   }
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / static_cast<float>(part) + eps);
-  for (int c = lane; c < part; c += 32) {
-    float v = yr[c];
-    const float gv = gate_fn(gr[c], gate_act);
-    const float wv = w[shared_w ? c : p * part + c];
-    v = gate_first ? (v * gv) * r * wv : v * r * wv * gv;
-    st(out, t * so + static_cast<long>(p) * part + c, scale * v);
+  for (int c = lane * V; c < part; c += 32 * V) {
+    float v[V], gv[V], wv[V];
+    ldv<V>(yr + c, v);
+    ldv<V>(gr + c, gv);
+    ldv<V>(w + (shared_w ? c : p * part + c), wv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float gg = gate_fn(gv[i], gate_act);
+      v[i] = scale * (gate_first ? (v[i] * gg) * r * wv[i] : v[i] * r * wv[i] * gg);
+    }
+    stv<V>(out + t * so + static_cast<long>(p) * part + c, v);
   }
 }
 
 // one block per (token, part): wide parts (a warp alone would walk them serially)
-template <typename OT>
+template <typename OT, int V>
 __global__ void gated_part_rmsnorm_block_kernel(const float* __restrict__ y, long sy, const float* __restrict__ gate, long sg,
                                                 const float* __restrict__ w, int shared_w, int part, int gate_act, int gate_first,
                                                 float eps, float scale, OT* __restrict__ out, long so, int nparts) {
@@ -130,10 +186,15 @@ __global__ void gated_part_rmsnorm_block_kernel(const float* __restrict__ y, lon
   const float* yr = y + t * sy + static_cast<long>(p) * part;
   const float* gr = gate + t * sg + static_cast<long>(p) * part;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < part; c += blockDim.x) {
-    float v = yr[c];
-    if (gate_first) v *= gate_fn(gr[c], gate_act);
-    ss += v * v;
+  for (int c = threadIdx.x * V; c < part; c += blockDim.x * V) {
+    float v[V], gv[V];
+    ldv<V>(yr + c, v);
+    if (gate_first) ldv<V>(gr + c, gv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      if (gate_first) v[i] *= gate_fn(gv[i], gate_act);
+      ss += v[i] * v[i];
+    }
   }
   ss = warp_sum(ss);
   if (lane == 0) red[wi] = ss;
@@ -141,15 +202,41 @@ __global__ void gated_part_rmsnorm_block_kernel(const float* __restrict__ y, lon
   float tot = 0.f;
   for (int i = 0; i < nw; ++i) tot += red[i];
   const float r = 1.f / sqrtf(tot / static_cast<float>(part) + eps);
-  for (int c = threadIdx.x; c < part; c += blockDim.x) {
-    float v = yr[c];
-    const float gv = gate_fn(gr[c], gate_act);
-    const float wv = w[shared_w ? c : p * part + c];
-    v = gate_first ? (v * gv) * r * wv : v * r * wv * gv;
-    st(out, t * so + static_cast<long>(p) * part + c, scale * v);
+  for (int c = threadIdx.x * V; c < part; c += blockDim.x * V) {
+    float v[V], gv[V], wv[V];
+    ldv<V>(yr + c, v);
+    ldv<V>(gr + c, gv);
+    ldv<V>(w + (shared_w ? c : p * part + c), wv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float gg = gate_fn(gv[i], gate_act);
+      v[i] = scale * (gate_first ? (v[i] * gg) * r * wv[i] : v[i] * r * wv[i] * gg);
+    }
+    stv<V>(out + t * so + static_cast<long>(p) * part + c, v);
   }
 }
 
+}  // namespace
+
+namespace {
+template <typename OT, int V>
+cudaError_t launch_gated_norm(const float* y, long sy, const float* gate, long sg, const float* w, int shared_w, int part, int gate_act,
+                              int gate_first, float eps, float scale, OT* out, long so, int T, int nparts, cudaStream_t s) {
+  const long warps = static_cast<long>(T) * nparts;
+  if (part >= 256) {
+    const int th = part >= 1024 * V / 4 ? 256 : 128;
+    gated_part_rmsnorm_block_kernel<OT, V><<<static_cast<unsigned>(warps), th, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act,
+                                                                                      gate_first, eps, scale, out, so, nparts);
+  } else {
+    gated_part_rmsnorm_kernel<OT, V><<<static_cast<unsigned>((warps + 3) / 4), 128, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act,
+                                                                                            gate_first, eps, scale, out, so, T, nparts);
+  }
+  return cudaGetLastError();
+}
+}  // namespace
+
+namespace {
+inline bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
 }  // namespace
 
 extern "C" {
@@ -180,6 +267,16 @@ cudaError_t nrl_stream_norm(float* results, long stride_r, int i, const float* o
 
 cudaError_t nrl_act_cols(const float* in, long si, void* out, long so, int out_f32, int act, int T, int C, cudaStream_t s) {
   if (T <= 0 || C <= 0) return cudaSuccess;
+  const size_t out_align = out_f32 ? 16 : 8;
+  if (C % 4 == 0 && si % 4 == 0 && so % 4 == 0 && aligned(in, 16) && aligned(out, out_align)) {
+    const long n = static_cast<long>(T) * (C / 4);
+    const int blocks = static_cast<int>((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (out_f32)
+      act_cols_vec4_kernel<float><<<blocks, 256, 0, s>>>(in, si, static_cast<float*>(out), so, act, T, C / 4);
+    else
+      act_cols_vec4_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(in, si, static_cast<__nv_bfloat16*>(out), so, act, T, C / 4);
+    return cudaGetLastError();
+  }
   const long n = static_cast<long>(T) * C;
   const int blocks = static_cast<int>((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   if (out_f32)
@@ -195,25 +292,18 @@ cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, l
   if (T <= 0 || n <= 0) return cudaSuccess;
   if (part <= 0 || n % part != 0) return cudaErrorInvalidValue;
   const int nparts = n / part;
-  const long warps = static_cast<long>(T) * nparts;
-  if (part >= 256) {
-    const int th = part >= 512 ? 256 : 128;
-    if (out_f32)
-      gated_part_rmsnorm_block_kernel<float><<<static_cast<unsigned>(warps), th, 0, s>>>(
-          y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale, static_cast<float*>(out), so, nparts);
-    else
-      gated_part_rmsnorm_block_kernel<__nv_bfloat16><<<static_cast<unsigned>(warps), th, 0, s>>>(
-          y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale, static_cast<__nv_bfloat16*>(out), so, nparts);
-    return cudaGetLastError();
+  const bool vec = part % 4 == 0 && sy % 4 == 0 && sg % 4 == 0 && so % 4 == 0 && aligned(y, 16) && aligned(gate, 16) && aligned(w, 16) &&
+                   aligned(out, out_f32 ? 16 : 8);
+#define NRL_GN(OT_, V_)                                                                                                            \
+  return launch_gated_norm<OT_, V_>(y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale, static_cast<OT_*>(out), so, T, \
+                                    nparts, s)
+  if (out_f32) {
+    if (vec) NRL_GN(float, 4);
+    NRL_GN(float, 1);
   }
-  const int blocks = static_cast<int>((warps + 3) / 4);
-  if (out_f32)
-    gated_part_rmsnorm_kernel<float><<<blocks, 128, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps, scale,
-                                                            static_cast<float*>(out), so, T, nparts);
-  else
-    gated_part_rmsnorm_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(y, sy, gate, sg, w, shared_w, part, gate_act, gate_first, eps,
-                                                                    scale, static_cast<__nv_bfloat16*>(out), so, T, nparts);
-  return cudaGetLastError();
+  if (vec) NRL_GN(__nv_bfloat16, 4);
+  NRL_GN(__nv_bfloat16, 1);
+#undef NRL_GN
 }
 
 }  // extern "C"
