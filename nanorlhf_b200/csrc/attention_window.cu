@@ -371,9 +371,13 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
   if (T <= 0) return cudaSuccess;
   if (Dv > 32 * kMaxDvPerLane || Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
   // prompt portions over bf16 pages: tensor cores
-  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page))
+  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page)) {
+    if (single_token && nsplit >= 1 && part != nullptr)
+      return nrl_window_attention_decode(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out,
+                                         so, T, Hq, Hkv, D, Dv, page, nsplit, part, s);
     return nrl_window_attention_mma(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so,
-                                    T, Hq, Hkv, D, Dv, page, single_token, single_token ? nsplit : 1, part, s);
+                                    T, Hq, Hkv, D, Dv, page, single_token, 1, nullptr, s);
+  }
   if (impl == 3) return cudaErrorInvalidValue;
   if (impl != 2 && Dv <= 128 && Dv % 4 == 0 && D <= 512) {
     // queries per block: the heads of one key/value head for single-token steps, 16 (tokens x heads) when entries hold runs

@@ -55,12 +55,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// one 64-key block of K or V into shared memory: rows = keys kb .. kb + 63 of the sequence, `width` real columns of `wp`
+// one 64-key block of K or V into shared memory: rows = keys kb .. kb + 63 of the sequence, `width` real columns of WP
+// (WP / 8 is a power of two: the index arithmetic is shifts)
+template <int WP>
 __device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int* bt, int Hkv, int g, int kb,
-                                              int hi, int width, int wp) {
-  const int chunks = wp / 8, ld = wp + kPad;
+                                              int hi, int width) {
+  constexpr int chunks = WP / 8, ld = WP + kPad;
+#pragma unroll
   for (int idx = threadIdx.x; idx < kBN * chunks; idx += kThreads) {
-    const int key = idx / chunks, ch = idx - key * chunks;
+    const int key = idx / chunks, ch = idx % chunks;
     const int j = kb + key;
     __nv_bfloat16* d = dst + key * ld + ch * 8;
     if (j <= hi && ch * 8 < width) {
@@ -152,15 +155,15 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     const int ib0 = split * per_split, ib1 = min(nblk, ib0 + per_split);
     __syncthreads();                                       // the previous run's last block has been consumed
     if (ib0 < ib1) {
-      load_kv_block(sK, k_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, D, DP);
-      load_kv_block(sV, v_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, Dv, DVP);
+      load_kv_block<DP>(sK, k_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, D);
+      load_kv_block<DVP>(sV, v_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, Dv);
       cp_commit();
     }
     for (int ib = ib0; ib < ib1; ++ib) {
       const int kb = kb0 + ib * kBN, buf = (ib - ib0) & 1;
       if (ib + 1 < ib1) {
-        load_kv_block(sK + (buf ^ 1) * kBN * LDK, k_cache, bt, Hkv, g, kb + kBN, hi, D, DP);
-        load_kv_block(sV + (buf ^ 1) * kBN * LDV, v_cache, bt, Hkv, g, kb + kBN, hi, Dv, DVP);
+        load_kv_block<DP>(sK + (buf ^ 1) * kBN * LDK, k_cache, bt, Hkv, g, kb + kBN, hi, D);
+        load_kv_block<DVP>(sV + (buf ^ 1) * kBN * LDV, v_cache, bt, Hkv, g, kb + kBN, hi, Dv);
         cp_commit();
         cp_wait<1>();
       } else {
@@ -295,6 +298,178 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Steps of single tokens: the work is reading the window's pages once, so every WARP walks its own run of pages with its
+// own cp.async ring (kDecStages pages of 16 keys in flight, no block barrier in the loop) for the <= 16 query heads that
+// share the key/value head, and leaves (O, max, l) of its run as one part; the merge launch combines the parts.
+// grid (token, key/value head, split); parts per (token, head) = 4 warps x splits.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kDecStages = 3;
+
+template <int KS, int NV>
+__global__ void __launch_bounds__(kThreads)
+window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
+                               const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+                               const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale,
+                               float* __restrict__ part, int Hq, int Hkv, int D, int Dv, int nsplit) {
+  constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
+  constexpr int kStageElems = 16 * LDK + 16 * LDV;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][LDK]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+  __nv_bfloat16* ring = sQ + 16 * LDK + w * kDecStages * kStageElems;        // this warp's [kDecStages]{K [16][LDK], V [16][LDV]}
+  const long t = blockIdx.x;
+  const int g = blockIdx.y, split = blockIdx.z, per_g = Hq / Hkv, h0 = g * per_g;
+  const int nparts = nsplit * 4, pi = split * 4 + w;
+
+  for (int idx = threadIdx.x; idx < 16 * DP; idx += kThreads) {
+    const int r = idx / DP, c = idx - r * DP;
+    float v = 0.f;
+    if (r < per_g && c < D) v = q[t * sq + static_cast<long>(h0 + r) * D + c];
+    sQ[r * LDK + c] = __float2bfloat16_rn(v);
+  }
+  __syncthreads();
+  uint32_t qf[KS][4];
+  {
+    const int m = lane >> 3, rr = (m & 1) * 8 + (lane & 7);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) ldsm_x4(smem_u32(sQ + rr * LDK + ks * 16 + (m >> 1) * 8), qf[ks]);
+  }
+  const int p = pos[t];
+  const int lo = max(0, p - window + 1);
+  const int* bt = block_table + static_cast<long>(tok_entry[t]) * max_blocks;
+  const int pg_first = lo >> 4, npages = (p >> 4) - pg_first + 1;
+  const int per_part = (npages + nparts - 1) / nparts;
+  const int pg0 = pg_first + pi * per_part, pg1 = min(pg_first + npages, pg0 + per_part);     // this warp's pages [pg0, pg1)
+
+  auto load_page = [&](int stage, int pg) {
+    __nv_bfloat16* sK = ring + stage * kStageElems;
+    __nv_bfloat16* sV = sK + 16 * LDK;
+    const long cell0 = (static_cast<long>(bt[pg]) * Hkv + g) * 16;
+    constexpr int kch = DP / 8, vch = DVP / 8;              // powers of two: shifts
+#pragma unroll
+    for (int idx = lane; idx < 16 * kch; idx += 32) {
+      const int key = idx / kch, ch = idx % kch;
+      __nv_bfloat16* d = sK + key * LDK + ch * 8;
+      if (pg * 16 + key <= p && ch * 8 < D) cp_async16(smem_u32(d), k_cache + (cell0 + key) * D + ch * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);          // padding, or cells after the token
+    }
+#pragma unroll
+    for (int idx = lane; idx < 16 * vch; idx += 32) {
+      const int key = idx / vch, ch = idx % vch;
+      __nv_bfloat16* d = sV + key * LDV + ch * 8;
+      if (pg * 16 + key <= p && ch * 8 < Dv) cp_async16(smem_u32(d), v_cache + (cell0 + key) * Dv + ch * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+
+  float o[2 * NV][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl2 = scale * 1.4426950408889634f;
+#pragma unroll
+  for (int i = 0; i < kDecStages - 1; ++i) {
+    if (pg0 + i < pg1) load_page(i, pg0 + i);
+    cp_commit();
+  }
+  for (int pg = pg0; pg < pg1; ++pg) {
+    const int stage = (pg - pg0) % kDecStages;
+    if (pg + kDecStages - 1 < pg1) load_page((pg - pg0 + kDecStages - 1) % kDecStages, pg + kDecStages - 1);
+    cp_commit();
+    cp_wait<kDecStages - 1>();
+    __syncwarp();
+    const __nv_bfloat16* bK = ring + stage * kStageElems;
+    const __nv_bfloat16* bV = bK + 16 * LDK;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const int m = lane >> 3;
+      const int krow = (m >> 1) * 8 + (lane & 7), kcol = (m & 1) * 8;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t b[4];
+        ldsm_x4(smem_u32(bK + krow * LDK + ks * 16 + kcol), b);
+        mma_bf16(s[0], qf[ks], b[0], b[1]);
+        mma_bf16(s[1], qf[ks], b[2], b[3]);
+      }
+    }
+    float mrow[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = pg * 16 + n * 8 + 2 * tq + (i & 1);
+        const float sc = (j <= p && j >= lo) ? s[n][i] * sl2 : -INFINITY;
+        s[n][i] = sc;
+        mrow[i >> 1] = fmaxf(mrow[i >> 1], sc);
+      }
+    }
+    float corr[2], m_sub[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      mrow[hf] = fmaxf(mrow[hf], __shfl_xor_sync(0xffffffffu, mrow[hf], 1));
+      mrow[hf] = fmaxf(mrow[hf], __shfl_xor_sync(0xffffffffu, mrow[hf], 2));
+      const float mn = fmaxf(m_run[hf], mrow[hf]);
+      corr[hf] = mn == -INFINITY ? 1.f : ex2(m_run[hf] - mn);
+      m_run[hf] = mn;
+      m_sub[hf] = mn == -INFINITY ? 0.f : mn;
+      l_run[hf] *= corr[hf];
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float pr = ex2(s[n][i] - m_sub[i >> 1]);
+        s[n][i] = pr;
+        l_run[i >> 1] += pr;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[0][0], s[0][1]);
+      pa[1] = pack_bf16(s[0][2], s[0][3]);
+      pa[2] = pack_bf16(s[1][0], s[1][1]);
+      pa[3] = pack_bf16(s[1][2], s[1][3]);
+      const int m = lane >> 3;
+      const int vrow = (m & 1) * 8 + (lane & 7), vcol = (m >> 1) * 8;
+#pragma unroll
+      for (int nv = 0; nv < NV; ++nv) {
+        uint32_t b[4];
+        ldsm_x4_t(smem_u32(bV + vrow * LDV + nv * 16 + vcol), b);
+        mma_bf16(o[2 * nv], pa, b[0], b[1]);
+        mma_bf16(o[2 * nv + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncwarp();                                          // the stage may be filled again
+  }
+  cp_wait<0>();
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    float l = l_run[hf];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int r = gq + hf * 8;
+    if (r >= per_g) continue;
+    float* pd = part + ((t * Hq + h0 + r) * nparts + pi) * (Dv + 2);
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i) {
+      const int c = i * 8 + 2 * tq;
+      if (c < Dv) {
+        pd[c] = o[i][2 * hf];
+        pd[c + 1] = o[i][2 * hf + 1];
+      }
+    }
+    if (tq == 0) {
+      pd[Dv] = m_run[hf];
+      pd[Dv + 1] = l;
+    }
+  }
+}
+
 // block per (token, query head): out = out_scale * sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s
 __global__ void window_attention_merge_kernel(const float* __restrict__ part, int nsplit, int Hq, int Dv, float out_scale,
                                               __nv_bfloat16* __restrict__ out, long so) {
@@ -346,19 +521,61 @@ cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_c
   return cudaGetLastError();
 }
 
+template <int KS, int NV>
+cudaError_t launch_decode(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+                          const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T,
+                          int Hq, int Hkv, int D, int Dv, int nsplit, float* part, cudaStream_t s) {
+  constexpr size_t smem = sizeof(__nv_bfloat16) * (16 * (16 * KS + kPad) +
+                                                   4 * kDecStages * (16 * (16 * KS + kPad) + 16 * (16 * NV + kPad)));
+  auto kern = window_attention_decode_kernel<KS, NV>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<dim3(T, Hkv, nsplit), kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(k_cache),
+                                                    static_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks, tok_entry, pos,
+                                                    window, scale, part, Hq, Hkv, D, Dv, nsplit);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  window_attention_merge_kernel<<<dim3(T, Hq), Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128, 0, s>>>(part, nsplit * 4, Hq, Dv, out_scale,
+                                                                                          static_cast<__nv_bfloat16*>(out), so);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 extern "C" {
 
+// Steps of single tokens (<= 16 query heads per key/value head): every warp walks its own pages and leaves a part.
+// `part`: float [T, Hq, 4 nsplit, Dv + 2].
+cudaError_t nrl_window_attention_decode(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
+                                        int max_blocks, const int* tok_entry, const int* pos, int window, float scale,
+                                        float out_scale, void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page,
+                                        int nsplit, float* part, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (!nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) || Hq / Hkv > 16 || window < 1 || nsplit < 1 || part == nullptr)
+    return cudaErrorInvalidValue;
+  const int ks = D <= 32 ? 2 : D <= 64 ? 4 : 8, nv = Dv <= 32 ? 2 : Dv <= 64 ? 4 : 8;
+#define NRL_WD(KS_, NV_)                                                                                                         \
+  if (ks == KS_ && nv == NV_)                                                                                                    \
+    return launch_decode<KS_, NV_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so, \
+                                   T, Hq, Hkv, D, Dv, nsplit, part, s);
+  NRL_WD(2, 2) NRL_WD(2, 4) NRL_WD(2, 8) NRL_WD(4, 2) NRL_WD(4, 4) NRL_WD(4, 8) NRL_WD(8, 2) NRL_WD(8, 4) NRL_WD(8, 8)
+#undef NRL_WD
+  return cudaErrorInvalidValue;
+}
+
 // In how many parts a step of single tokens walks its keys so that the grid fills the GPU (1: no parts, no merge).
 int nrl_window_attention_splits(int T, int Hq, int Hkv, int window, int max_blocks, int page) {
-  if (Hkv <= 0 || Hq / Hkv > kBM) return 1;
+  if (Hkv <= 0 || Hq / Hkv > 16) return 0;                  // 0: the single-token kernel does not take this shape
   const long keys = static_cast<long>(max_blocks) * page < window ? static_cast<long>(max_blocks) * page : window;
-  const int nblk = static_cast<int>((keys + kBN - 1) / kBN) + 1;
+  const long pages = (keys + 15) / 16 + 1;
   const long blocks = static_cast<long>(T) * Hkv;
-  long want = (2 * 148 + blocks - 1) / blocks;
-  if (want > nblk) want = nblk;
-  if (want > 16) want = 16;
+  long want = (2 * 148 + blocks - 1) / blocks;              // two blocks per SM
+  if (want > pages / 8) want = pages / 8;                   // at least two pages per warp
+  if (want > 8) want = 8;
   return want < 1 ? 1 : static_cast<int>(want);
 }
 

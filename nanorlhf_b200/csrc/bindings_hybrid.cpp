@@ -173,18 +173,18 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   TORCH_CHECK(block_table.dim() == 2 && out.dim() == 2 && out.size(0) == T && out.size(1) == static_cast<int64_t>(Hq) * Dv,
               "window_attention: shapes");
   // steps of single tokens on bf16 pages: cut the key walk into parts so that few sequences still fill the GPU
-  int nsplit = 1;
+  int nsplit = 0;
   Tensor part;
   if (single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
       nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page)) {
     nsplit = nrl_window_attention_splits(T, Hq, Hkv, static_cast<int>(window), static_cast<int>(block_table.size(1)), page);
-    if (nsplit > 1) part = at::empty({T, Hq, nsplit, Dv + 2}, q.options().dtype(at::kFloat));
+    if (nsplit >= 1) part = at::empty({T, Hq, 4 * nsplit, Dv + 2}, q.options().dtype(at::kFloat));
   }
   check(nrl_window_attention(f32(q, "q"), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), typed(k_cache, "k_cache"),
                              i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
                              i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
                              out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
-                             nsplit, nsplit > 1 ? part.data_ptr<float>() : nullptr, cur_stream()),
+                             nsplit, nsplit >= 1 ? part.data_ptr<float>() : nullptr, cur_stream()),
         "window_attention");
 }
 

@@ -77,15 +77,19 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D,
                                  int Dv, int page, int single_token, int impl, int nsplit, float* part, cudaStream_t s);
-// `nsplit` > 1 with `part` float [T, Hq, nsplit, Dv + 2] (steps of single tokens on the tensor-core kernel only): the key walk
-// is cut into nsplit parts that run as separate blocks and are merged by a second launch; nrl_window_attention_splits
-// proposes the count.
+// `nsplit` >= 1 with `part` float [T, Hq, 4 nsplit, Dv + 2] (steps of single tokens over bf16 pages): every warp of nsplit
+// blocks per (token, key/value head) walks its own pages and a second launch merges the parts; nrl_window_attention_splits
+// proposes the count (0: the shape does not fit).
 // `impl`: 0 picks by shape and step kind, 1 the scalar tile kernel, 2 one block per (token, head), 3 the tensor-core kernel.
 
 // Tensor-core kernel for prompt portions over bf16 pages of 16 tokens (attention_window_mma.cu); `_fits` says whether the
 // shapes and the output's alignment allow it.
 int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int D, int Dv, int page);
 int nrl_window_attention_splits(int T, int Hq, int Hkv, int window, int max_blocks, int page);
+cudaError_t nrl_window_attention_decode(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
+                                        int max_blocks, const int* tok_entry, const int* pos, int window, float scale,
+                                        float out_scale, void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page,
+                                        int nsplit, float* part, cudaStream_t s);
 cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
