@@ -376,7 +376,7 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
       return nrl_window_attention_decode(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out,
                                          so, T, Hq, Hkv, D, Dv, page, nsplit, part, s);
     return nrl_window_attention_mma(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so,
-                                    T, Hq, Hkv, D, Dv, page, single_token, 1, nullptr, s);
+                                    T, Hq, Hkv, D, Dv, page, single_token, s);
   }
   if (impl == 3) return cudaErrorInvalidValue;
   if (impl != 2 && Dv <= 128 && Dv % 4 == 0 && D <= 512) {

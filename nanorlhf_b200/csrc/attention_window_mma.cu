@@ -1,13 +1,15 @@
-// Sliding-window attention for prompt portions on the tensor cores, reading the 16-token bf16 pages in place.
+// Sliding-window attention on the tensor cores, reading the 16-token bf16 pages in place.
 //
-// A block owns 64 query rows that share one key/value head -- QT consecutive tokens x HB query heads -- as four warps of 16
-// rows, and walks the keys its rows can see in blocks of 64 (four pages), double buffered through shared memory with
-// cp.async.  Per block:  S = Q K^T (bf16 operands, float accumulators), scores scaled and masked in float (key j is seen
-// by the query at position p when p - window < j <= p), online softmax in float (base 2, ex2.approx), P rounded to bf16 only as the operand
-// of O += P V (float accumulators).  Query / key size D and value size Dv are runtime values; the templates fix the padded
-// sizes (multiples of 32 up to 128), the padding is zero-filled in shared memory.  Tokens of different sequences that fall
-// into one tile are handled one run after the other over the same accumulators (a row belongs to one run only).
-// Compiled WITHOUT fast-math.
+// Prompt portions (window_attention_mma_kernel): a block owns 64 query rows that share one key/value head -- QT
+// consecutive tokens x HB query heads -- as four warps of 16 rows, and walks the keys its rows can see in blocks of 64
+// (four pages), double buffered through shared memory with cp.async.  Per block: S = Q K^T (bf16 operands, float
+// accumulators); scores scaled and masked in float (key j is seen by the query at position p when p - window < j <= p;
+// blocks that no window edge crosses skip the mask); online softmax in float, base 2 with ex2.approx; P is rounded to bf16
+// only as the operand of O += P V (float accumulators).  Tokens of different sequences that fall into one tile are handled
+// one run after the other over the same accumulators (a row belongs to one run only).
+// Steps of single tokens (window_attention_decode_kernel): every warp walks its own pages; see there.
+// Query / key size D and value size Dv are runtime values (multiples of 8 up to 128); the templates fix the padded sizes
+// (32, 64 or 128), the padding is zero-filled in shared memory.  Compiled WITHOUT fast-math.
 #include <cuda_bf16.h>
 
 #include <cstdint>
@@ -80,15 +82,13 @@ __global__ void __launch_bounds__(kThreads)
 window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
                             const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                             const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale, float out_scale,
-                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT,
-                            int nsplit, float* __restrict__ part) {
+                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT) {
   constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kBM][LDK]
   __nv_bfloat16* sK = sQ + kBM * LDK;                                         // [2][kBN][LDK]
   __nv_bfloat16* sV = sK + 2 * kBN * LDK;                                     // [2][kBN][LDV]
-  // nsplit > 1 (steps of single tokens, all heads of the group in one block): blockIdx.z = which part of the key walk
-  const int zb = nsplit > 1 ? 0 : static_cast<int>(blockIdx.z), split = nsplit > 1 ? static_cast<int>(blockIdx.z) : 0;
+  const int zb = static_cast<int>(blockIdx.z);
   const int g = blockIdx.y, per_g = Hq / Hkv, h0 = g * per_g + zb * HB;
   const int hb = min(HB, per_g - zb * HB);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
@@ -151,17 +151,13 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     const bool warp_full = wt_lo >= t && wt_hi < tn;       // every row of the warp that holds a query belongs to this run
     const int whi = p_first + (wb - t), wlo = p_first + (wa - t) - window + 1;
 
-    const int per_split = (nblk + nsplit - 1) / nsplit;
-    const int ib0 = split * per_split, ib1 = min(nblk, ib0 + per_split);
     __syncthreads();                                       // the previous run's last block has been consumed
-    if (ib0 < ib1) {
-      load_kv_block<DP>(sK, k_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, D);
-      load_kv_block<DVP>(sV, v_cache, bt, Hkv, g, kb0 + ib0 * kBN, hi, Dv);
-      cp_commit();
-    }
-    for (int ib = ib0; ib < ib1; ++ib) {
-      const int kb = kb0 + ib * kBN, buf = (ib - ib0) & 1;
-      if (ib + 1 < ib1) {
+    load_kv_block<DP>(sK, k_cache, bt, Hkv, g, kb0, hi, D);
+    load_kv_block<DVP>(sV, v_cache, bt, Hkv, g, kb0, hi, Dv);
+    cp_commit();
+    for (int ib = 0; ib < nblk; ++ib) {
+      const int kb = kb0 + ib * kBN, buf = ib & 1;
+      if (ib + 1 < nblk) {
         load_kv_block<DP>(sK + (buf ^ 1) * kBN * LDK, k_cache, bt, Hkv, g, kb + kBN, hi, D);
         load_kv_block<DVP>(sV + (buf ^ 1) * kBN * LDV, v_cache, bt, Hkv, g, kb + kBN, hi, Dv);
         cp_commit();
@@ -264,7 +260,7 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     }
     t = tn;
   }
-  // ---- out = out_scale * O / l, or this part's (O, max, l) for the merge ----
+  // ---- out = out_scale * O / l ----
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     float l = l_run[hf];
@@ -272,22 +268,6 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     if (!row_ok[hf]) continue;
     const int r = w * 16 + gq + hf * 8;
-    if (nsplit > 1) {
-      float* pd = part + ((static_cast<long>(row_t[hf]) * Hq + h0 + r % HB) * nsplit + split) * (Dv + 2);
-#pragma unroll
-      for (int i = 0; i < 2 * NV; ++i) {
-        const int c = i * 8 + 2 * tq;
-        if (c < Dv) {
-          pd[c] = o[i][2 * hf];
-          pd[c + 1] = o[i][2 * hf + 1];
-        }
-      }
-      if (tq == 0) {
-        pd[Dv] = m_run[hf];
-        pd[Dv + 1] = l;
-      }
-      continue;
-    }
     __nv_bfloat16* dst = out + static_cast<long>(row_t[hf]) * so + static_cast<long>(h0 + r % HB) * Dv;
     const float f = out_scale / l;
 #pragma unroll
@@ -496,9 +476,9 @@ __global__ void window_attention_merge_kernel(const float* __restrict__ part, in
 template <int KS, int NV>
 cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                    const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T, int Hq,
-                   int Hkv, int D, int Dv, int single_token, int nsplit, float* part, cudaStream_t s) {
+                   int Hkv, int D, int Dv, int single_token, cudaStream_t s) {
   const int per_g = Hq / Hkv;
-  // a step of single tokens: one token per block (every token walks its own sequence; more blocks, shorter walks)
+  // a step of single tokens that the per-warp kernel does not take: one token per block
   const int HB = per_g < kBM ? per_g : kBM, QT = single_token ? 1 : kBM / HB;
   constexpr size_t smem = sizeof(__nv_bfloat16) * (static_cast<size_t>(kBM) * (16 * KS + kPad) + 2 * kBN * (16 * KS + kPad) +
                                                    2 * kBN * (16 * NV + kPad));
@@ -509,15 +489,10 @@ cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_c
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  if (nsplit > 1 && (!single_token || per_g > kBM || part == nullptr)) return cudaErrorInvalidValue;
-  const dim3 grid((T + QT - 1) / QT, Hkv, nsplit > 1 ? nsplit : (per_g + HB - 1) / HB);
+  const dim3 grid((T + QT - 1) / QT, Hkv, (per_g + HB - 1) / HB);
   kern<<<grid, kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
                                     block_table, max_blocks, tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so,
-                                    T, Hq, Hkv, D, Dv, HB, QT, nsplit, part);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess || nsplit <= 1) return e;
-  window_attention_merge_kernel<<<dim3(T, Hq), Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128, 0, s>>>(part, nsplit, Hq, Dv, out_scale,
-                                                                                          static_cast<__nv_bfloat16*>(out), so);
+                                    T, Hq, Hkv, D, Dv, HB, QT);
   return cudaGetLastError();
 }
 
@@ -587,14 +562,14 @@ int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int
 cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
-                                     int nsplit, float* part, cudaStream_t s) {
+                                     cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
   if (!nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) || window < 1) return cudaErrorInvalidValue;
   const int ks = D <= 32 ? 2 : D <= 64 ? 4 : 8, nv = Dv <= 32 ? 2 : Dv <= 64 ? 4 : 8;
 #define NRL_WM(KS_, NV_)                                                                                                         \
   if (ks == KS_ && nv == NV_)                                                                                                    \
     return launch<KS_, NV_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so, T, Hq, \
-                            Hkv, D, Dv, single_token, nsplit, part, s);
+                            Hkv, D, Dv, single_token, s);
   NRL_WM(2, 2) NRL_WM(2, 4) NRL_WM(2, 8) NRL_WM(4, 2) NRL_WM(4, 4) NRL_WM(4, 8) NRL_WM(8, 2) NRL_WM(8, 4) NRL_WM(8, 8)
 #undef NRL_WM
   return cudaErrorInvalidValue;

@@ -93,5 +93,5 @@ cudaError_t nrl_window_attention_decode(const float* q, long sq, const void* k_c
 cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
-                                     int nsplit, float* part, cudaStream_t s);
+                                     cudaStream_t s);
 }

@@ -474,23 +474,34 @@ delta_scan_reg_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
 // ---------------------------------------------------------------------------------------------------------------------
 __host__ __device__ constexpr int col_min_threads(int rows) { return rows > 64 ? 64 : 32; }      // so that a thread stages few values per token
 
-template <int ROWS>
+// SPLIT (1 or 2) threads share a column: neighbouring lanes hold the upper and the lower half of its rows and add their
+// partial sums with one shuffle (more threads in flight and half the registers for 128-row states).  In shared memory a
+// staged vector is SPLIT segments of ROWS / SPLIT + 4 floats, so that the two halves read different banks.
+template <int ROWS, int SPLIT>
+struct ColStage {
+  static constexpr int RH = ROWS / SPLIT;                 // rows per thread
+  static constexpr int VL = SPLIT * (RH + 4);             // floats per staged vector
+  __host__ __device__ static constexpr int at(int d) { return (d / RH) * (RH + 4) + d % RH; }
+};
+
+template <int ROWS, int SPLIT>
 __global__ void __launch_bounds__(256)
 ssd_scan_col_kernel(const float* __restrict__ xbc, long sx, int col_b, int col_c, const float* __restrict__ dt_raw, long sd,
                     const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
                     float* __restrict__ state, float* __restrict__ y, const int* __restrict__ cu, const int* __restrict__ start,
                     const int* __restrict__ state_slot, int heads, int groups, int N, int P) {
-  constexpr int L = 2 * ROWS + 4;                // per token: B | C | dt, decay
+  using St = ColStage<ROWS, SPLIT>;
+  constexpr int RH = St::RH, VL = St::VL, L = 2 * VL + 4;  // per token: B | C | dt, decay
   constexpr int kStagePre = (2 * ROWS + col_min_threads(ROWS) - 1) / col_min_threads(ROWS);
   __shared__ __align__(16) float stage[2 * L];
   const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / groups);
-  const int tid = threadIdx.x, nth = blockDim.x, p = tid;
+  const int tid = threadIdx.x, nth = blockDim.x, p = tid / SPLIT, half = tid % SPLIT, r0 = half * RH;
   const bool live = p < P;
   float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * N * P;
   const bool carried = start[e] > 0;
-  float S[ROWS];
+  float S[RH];
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) S[i] = (live && i < N && carried) ? gS[static_cast<long>(i) * P + p] : 0.f;
+  for (int i = 0; i < RH; ++i) S[i] = (live && r0 + i < N && carried) ? gS[static_cast<long>(r0 + i) * P + p] : 0.f;
   const float negA = -expf(A_log[h]), dskip = Dskip[h], bias = dt_bias[h];
   const int t0 = cu[e], t1 = cu[e + 1];
   float pre[kStagePre], pre_x, pre_dt;
@@ -513,23 +524,23 @@ ssd_scan_col_kernel(const float* __restrict__ xbc, long sx, int col_b, int col_c
 #pragma unroll
     for (int i = 0; i < kStagePre; ++i) {
       const int idx = tid + i * nth;
-      if (idx < 2 * ROWS) v[idx] = pre[i];
+      if (idx < 2 * ROWS) v[(idx < ROWS ? 0 : VL) + St::at(idx < ROWS ? idx : idx - ROWS)] = pre[i];
     }
     if (tid == 0) {
       const float dt = softplus(pre_dt + bias);
-      v[2 * ROWS] = dt;
-      v[2 * ROWS + 1] = expf(negA * dt);
+      v[2 * VL] = dt;
+      v[2 * VL + 1] = expf(negA * dt);
     }
     const float x_cur = pre_x;
     __syncthreads();
     if (t + 1 < t1) fetch(t + 1);
-    const float dt = v[2 * ROWS], a = v[2 * ROWS + 1];
+    const float dt = v[2 * VL], a = v[2 * VL + 1];
     const float xs = dt * x_cur;
-    const float4* vB = reinterpret_cast<const float4*>(v);
-    const float4* vC = reinterpret_cast<const float4*>(v + ROWS);
+    const float4* vB = reinterpret_cast<const float4*>(v + half * (RH + 4));
+    const float4* vC = reinterpret_cast<const float4*>(v + VL + half * (RH + 4));
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < ROWS / 4; ++i) {
+    for (int i = 0; i < RH / 4; ++i) {
       const float4 b = vB[i], c = vC[i];
       S[4 * i] = a * S[4 * i] + b.x * xs;
       S[4 * i + 1] = a * S[4 * i + 1] + b.y * xs;
@@ -540,32 +551,35 @@ ssd_scan_col_kernel(const float* __restrict__ xbc, long sx, int col_b, int col_c
       acc[2] += S[4 * i + 2] * c.z;
       acc[3] += S[4 * i + 3] * c.w;
     }
-    if (live) y[static_cast<long>(t) * heads * P + h * P + p] = (acc[0] + acc[1]) + (acc[2] + acc[3]) + dskip * x_cur;
+    float tot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (SPLIT == 2) tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+    if (live && half == 0) y[static_cast<long>(t) * heads * P + h * P + p] = tot + dskip * x_cur;
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i)
-      if (i < N) gS[static_cast<long>(i) * P + p] = S[i];
+    for (int i = 0; i < RH; ++i)
+      if (r0 + i < N) gS[static_cast<long>(r0 + i) * P + p] = S[i];
   }
 }
 
-template <int ROWS>
+template <int ROWS, int SPLIT>
 __global__ void __launch_bounds__(256)
 delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col_v, const float* __restrict__ beta,
                       const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o, const int* __restrict__ cu,
                       const int* __restrict__ start, const int* __restrict__ state_slot, int heads, int kv_heads, int D, int Dv,
                       int per_channel) {
-  constexpr int L = 3 * ROWS + 4;                // per token: q | k | row decays | beta
+  using St = ColStage<ROWS, SPLIT>;
+  constexpr int RH = St::RH, VL = St::VL, L = 3 * VL;      // per token: q | k | row decays
   constexpr int kStagePre = (3 * ROWS + col_min_threads(ROWS) - 1) / col_min_threads(ROWS);
   __shared__ __align__(16) float stage[2 * L];
   const int e = blockIdx.x, h = blockIdx.y, g = h / (heads / kv_heads);
-  const int tid = threadIdx.x, nth = blockDim.x, c = tid;
+  const int tid = threadIdx.x, nth = blockDim.x, c = tid / SPLIT, half = tid % SPLIT, r0 = half * RH;
   const bool live = c < Dv;
   float* gS = state + (static_cast<long>(state_slot[e]) * heads + h) * D * Dv;
   const bool carried = start[e] > 0;
-  float S[ROWS];
+  float S[RH];
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) S[i] = (live && i < D && carried) ? gS[static_cast<long>(i) * Dv + c] : 0.f;
+  for (int i = 0; i < RH; ++i) S[i] = (live && r0 + i < D && carried) ? gS[static_cast<long>(r0 + i) * Dv + c] : 0.f;
   const int t0 = cu[e], t1 = cu[e + 1];
   const int nd = per_channel ? heads * D : heads;
   float pre[kStagePre], pre_v, pre_beta;
@@ -594,17 +608,17 @@ delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
 #pragma unroll
     for (int i = 0; i < kStagePre; ++i) {
       const int idx = tid + i * nth;
-      if (idx < 3 * ROWS) v[idx] = pre[i];
+      if (idx < 3 * ROWS) v[(idx / ROWS) * VL + St::at(idx % ROWS)] = pre[i];
     }
     const float v_cur = pre_v, b_cur = pre_beta;
     __syncthreads();
     if (t + 1 < t1) fetch(t + 1);
-    const float4* vq = reinterpret_cast<const float4*>(v);
-    const float4* vk = reinterpret_cast<const float4*>(v + ROWS);
-    const float4* vg = reinterpret_cast<const float4*>(v + 2 * ROWS);
+    const float4* vq = reinterpret_cast<const float4*>(v + half * (RH + 4));
+    const float4* vk = reinterpret_cast<const float4*>(v + VL + half * (RH + 4));
+    const float4* vg = reinterpret_cast<const float4*>(v + 2 * VL + half * (RH + 4));
     float pk[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < ROWS / 4; ++i) {                       // S <- g S;  S^T k
+    for (int i = 0; i < RH / 4; ++i) {                         // S <- g S;  S^T k
       const float4 gg = vg[i], kk = vk[i];
       S[4 * i] *= gg.x;
       S[4 * i + 1] *= gg.y;
@@ -615,10 +629,12 @@ delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
       pk[2] += S[4 * i + 2] * kk.z;
       pk[3] += S[4 * i + 3] * kk.w;
     }
-    const float u = b_cur * (v_cur - ((pk[0] + pk[1]) + (pk[2] + pk[3])));
+    float sk = (pk[0] + pk[1]) + (pk[2] + pk[3]);
+    if (SPLIT == 2) sk += __shfl_xor_sync(0xffffffffu, sk, 1);
+    const float u = b_cur * (v_cur - sk);
     float po[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < ROWS / 4; ++i) {                       // S <- S + k u^T;  o = S^T q sees this token's write
+    for (int i = 0; i < RH / 4; ++i) {                         // S <- S + k u^T;  o = S^T q sees this token's write
       const float4 kk = vk[i], qq = vq[i];
       S[4 * i] += kk.x * u;
       S[4 * i + 1] += kk.y * u;
@@ -629,22 +645,26 @@ delta_scan_col_kernel(const float* __restrict__ qkv, long sq, int col_k, int col
       po[2] += S[4 * i + 2] * qq.z;
       po[3] += S[4 * i + 3] * qq.w;
     }
-    if (live) o[static_cast<long>(t) * heads * Dv + h * Dv + c] = (po[0] + po[1]) + (po[2] + po[3]);
+    float so_ = (po[0] + po[1]) + (po[2] + po[3]);
+    if (SPLIT == 2) so_ += __shfl_xor_sync(0xffffffffu, so_, 1);
+    if (live && half == 0) o[static_cast<long>(t) * heads * Dv + h * Dv + c] = so_;
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i)
-      if (i < D) gS[static_cast<long>(i) * Dv + c] = S[i];
+    for (int i = 0; i < RH; ++i)
+      if (r0 + i < D) gS[static_cast<long>(r0 + i) * Dv + c] = S[i];
   }
 }
 
-// template size and block size of the column-resident kernels for a state of `rows` x `cols`; false when they do not fit
-bool pick_col_layout(int cols, int rows, int* rows_t, int* threads_out) {
+// template sizes and block size of the column-resident kernels for a state of `rows` x `cols`; false when they do not fit
+bool pick_col_layout(int cols, int rows, int* rows_t, int* split_out, int* threads_out) {
   if (rows > 128 || cols < 1 || cols > 256) return false;
   const int rt = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
-  int threads = ((cols + 31) / 32) * 32;
+  const int split = rt == 128 && cols <= 128 ? 2 : 1;      // 128 rows: two threads per column when the block allows
+  int threads = ((cols * split + 31) / 32) * 32;
   if (threads < col_min_threads(rt)) threads = col_min_threads(rt);
   *rows_t = rt;
+  *split_out = split;
   *threads_out = threads;
   return true;
 }
@@ -721,15 +741,15 @@ cudaError_t nrl_ssd_scan(const float* xbc, long sx, int col_b, int col_c, const 
   if (E <= 0) return cudaSuccess;
   if (P > 512 || heads % groups != 0 || impl < 0 || impl > 3) return cudaErrorInvalidValue;
   if (impl == 0 || impl == 1) {
-    int rt, threads;
-    if (pick_col_layout(P, N, &rt, &threads)) {
-#define NRL_SSDC(R_)                                                                                                               \
-  if (rt == R_) {                                                                                                                  \
-    ssd_scan_col_kernel<R_><<<dim3(E, heads), threads, 0, s>>>(xbc, sx, col_b, col_c, dt_raw, sd, dt_bias, A_log, Dskip, state, y, cu, \
-                                                               start, state_slot, heads, groups, N, P);                            \
+    int rt, split, threads;
+    if (pick_col_layout(P, N, &rt, &split, &threads)) {
+#define NRL_SSDC(R_, S_)                                                                                                           \
+  if (rt == R_ && split == S_) {                                                                                                   \
+    ssd_scan_col_kernel<R_, S_><<<dim3(E, heads), threads, 0, s>>>(xbc, sx, col_b, col_c, dt_raw, sd, dt_bias, A_log, Dskip, state, y, \
+                                                                   cu, start, state_slot, heads, groups, N, P);                    \
     return cudaGetLastError();                                                                                                     \
   }
-      NRL_SSDC(16) NRL_SSDC(32) NRL_SSDC(64) NRL_SSDC(128)
+      NRL_SSDC(16, 1) NRL_SSDC(32, 1) NRL_SSDC(64, 1) NRL_SSDC(128, 1) NRL_SSDC(128, 2)
 #undef NRL_SSDC
     }
     if (impl == 1) return cudaErrorInvalidValue;
@@ -780,15 +800,15 @@ cudaError_t nrl_delta_scan(const float* qkv, long sq, int col_k, int col_v, cons
   if (E <= 0) return cudaSuccess;
   if (Dv > 512 || heads % kv_heads != 0 || impl < 0 || impl > 3) return cudaErrorInvalidValue;
   if (impl == 0 || impl == 1) {
-    int rt, threads;
-    if (pick_col_layout(Dv, D, &rt, &threads)) {
-#define NRL_DELTAC(R_)                                                                                                             \
-  if (rt == R_) {                                                                                                                  \
-    delta_scan_col_kernel<R_><<<dim3(E, heads), threads, 0, s>>>(qkv, sq, col_k, col_v, beta, decay, state, o, cu, start, state_slot,  \
-                                                                 heads, kv_heads, D, Dv, per_channel);                             \
+    int rt, split, threads;
+    if (pick_col_layout(Dv, D, &rt, &split, &threads)) {
+#define NRL_DELTAC(R_, S_)                                                                                                         \
+  if (rt == R_ && split == S_) {                                                                                                   \
+    delta_scan_col_kernel<R_, S_><<<dim3(E, heads), threads, 0, s>>>(qkv, sq, col_k, col_v, beta, decay, state, o, cu, start,        \
+                                                                     state_slot, heads, kv_heads, D, Dv, per_channel);             \
     return cudaGetLastError();                                                                                                     \
   }
-      NRL_DELTAC(16) NRL_DELTAC(32) NRL_DELTAC(64) NRL_DELTAC(128)
+      NRL_DELTAC(16, 1) NRL_DELTAC(32, 1) NRL_DELTAC(64, 1) NRL_DELTAC(128, 1) NRL_DELTAC(128, 2)
 #undef NRL_DELTAC
     }
     if (impl == 1) return cudaErrorInvalidValue;
