@@ -26,7 +26,12 @@ def _peaks():
     return 6.65e12, 1.59e15, "fallback"
 
 
+SMALL = False          # --small: one warm-up and one timed launch per kernel (the target of profiler captures)
+
+
 def _time(fn, iters=10, warm=3):
+    if SMALL:
+        iters, warm = 1, 1
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -220,9 +225,14 @@ def kernels(width=2048, batch=16, prompt_len=2048, window=1024, decode_batch=256
     return out
 
 
-def main(quick: bool = False):
+def main(quick: bool = False, small: bool = False):
     from nanorlhf_b200.ops import native
     native.load()
+    if small:                                  # kernels only, on a case of a few hundred MB
+        global SMALL
+        SMALL = True
+        print(json.dumps({"bench": "serve-small", "kernels": kernels(width=1024, batch=8, prompt_len=1024, decode_batch=64, ctx=1024)}))
+        return None
     res = {"bench": "serve", "kernels": kernels(), "end_to_end": []}
     for width, layers, batch, plen in ((1024, 8, 32, 1024), (2048, 8, 16, 2048)) if not quick else ((1024, 4, 8, 512),):
         res["end_to_end"].append(end_to_end(width, layers, batch, plen))
@@ -232,4 +242,4 @@ def main(quick: bool = False):
 
 
 if __name__ == "__main__":
-    main(quick="--quick" in sys.argv)
+    main(quick="--quick" in sys.argv, small="--small" in sys.argv)

@@ -57,19 +57,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+__device__ __forceinline__ int sel4(const int (&v)[4], int i) { return i == 0 ? v[0] : i == 1 ? v[1] : i == 2 ? v[2] : v[3]; }
+
+// the four pages that hold keys kb .. kb + 63 of a sequence (0 where the sequence ends before)
+__device__ __forceinline__ void block_pages(const int* bt, int kb, int hi, int (&pg)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) pg[i] = kb + 16 * i <= hi ? bt[(kb >> 4) + i] : 0;
+}
+
 // one 64-key block of K or V into shared memory: rows = keys kb .. kb + 63 of the sequence, `width` real columns of WP
 // (WP / 8 is a power of two: the index arithmetic is shifts)
 template <int WP>
-__device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int* bt, int Hkv, int g, int kb,
+__device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfloat16* cache, const int (&pg)[4], int Hkv, int g, int kb,
                                               int hi, int width) {
   constexpr int chunks = WP / 8, ld = WP + kPad;
 #pragma unroll
   for (int idx = threadIdx.x; idx < kBN * chunks; idx += kThreads) {
     const int key = idx / chunks, ch = idx % chunks;
-    const int j = kb + key;
     __nv_bfloat16* d = dst + key * ld + ch * 8;
-    if (j <= hi && ch * 8 < width) {
-      const long cell = (static_cast<long>(bt[j >> 4]) * Hkv + g) * 16 + (j & 15);
+    if (kb + key <= hi && ch * 8 < width) {
+      const long cell = (static_cast<long>(sel4(pg, key >> 4)) * Hkv + g) * 16 + (key & 15);
       cp_async16(smem_u32(d), cache + cell * width + ch * 8);
     } else {
       *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
@@ -78,16 +85,16 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfl
 }
 
 template <int KS, int NV>      // padded D = 16 KS, padded Dv = 16 NV
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
                             const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                             const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale, float out_scale,
                             __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT) {
   constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [kBM][LDK]
-  __nv_bfloat16* sK = sQ + kBM * LDK;                                         // [2][kBN][LDK]
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [2][kBN][LDK]
   __nv_bfloat16* sV = sK + 2 * kBN * LDK;                                     // [2][kBN][LDV]
+  __nv_bfloat16* sQ = sK + kBN * LDK;     // [kBM][LDK]: lives in K buffer 1, which is first filled after the queries left for registers
   const int zb = static_cast<int>(blockIdx.z);
   const int g = blockIdx.y, per_g = Hq / Hkv, h0 = g * per_g + zb * HB;
   const int hb = min(HB, per_g - zb * HB);
@@ -152,15 +159,19 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     const int whi = p_first + (wb - t), wlo = p_first + (wa - t) - window + 1;
 
     __syncthreads();                                       // the previous run's last block has been consumed
-    load_kv_block<DP>(sK, k_cache, bt, Hkv, g, kb0, hi, D);
-    load_kv_block<DVP>(sV, v_cache, bt, Hkv, g, kb0, hi, Dv);
+    int pg[4];
+    block_pages(bt, kb0, hi, pg);
+    load_kv_block<DP>(sK, k_cache, pg, Hkv, g, kb0, hi, D);
+    load_kv_block<DVP>(sV, v_cache, pg, Hkv, g, kb0, hi, Dv);
     cp_commit();
+    if (nblk > 1) block_pages(bt, kb0 + kBN, hi, pg);       // page ids are fetched a block ahead of their use
     for (int ib = 0; ib < nblk; ++ib) {
       const int kb = kb0 + ib * kBN, buf = ib & 1;
       if (ib + 1 < nblk) {
-        load_kv_block<DP>(sK + (buf ^ 1) * kBN * LDK, k_cache, bt, Hkv, g, kb + kBN, hi, D);
-        load_kv_block<DVP>(sV + (buf ^ 1) * kBN * LDV, v_cache, bt, Hkv, g, kb + kBN, hi, Dv);
+        load_kv_block<DP>(sK + (buf ^ 1) * kBN * LDK, k_cache, pg, Hkv, g, kb + kBN, hi, D);
+        load_kv_block<DVP>(sV + (buf ^ 1) * kBN * LDV, v_cache, pg, Hkv, g, kb + kBN, hi, Dv);
         cp_commit();
+        if (ib + 2 < nblk) block_pages(bt, kb + 2 * kBN, hi, pg);
         cp_wait<1>();
       } else {
         cp_wait<0>();
@@ -480,8 +491,8 @@ cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_c
   const int per_g = Hq / Hkv;
   // a step of single tokens that the per-warp kernel does not take: one token per block
   const int HB = per_g < kBM ? per_g : kBM, QT = single_token ? 1 : kBM / HB;
-  constexpr size_t smem = sizeof(__nv_bfloat16) * (static_cast<size_t>(kBM) * (16 * KS + kPad) + 2 * kBN * (16 * KS + kPad) +
-                                                   2 * kBN * (16 * NV + kPad));
+  static_assert(kBM == kBN, "the query tile borrows a key buffer");
+  constexpr size_t smem = sizeof(__nv_bfloat16) * (2 * kBN * (16 * KS + kPad) + 2 * kBN * (16 * NV + kPad));
   auto kern = window_attention_mma_kernel<KS, NV>;
   static bool configured = false;
   if (!configured) {
