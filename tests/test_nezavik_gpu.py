@@ -76,6 +76,9 @@ SHAPES = {
     "single_heads": dict(layers=("delta", "parallel", "channel_delta"),
                          sizes=dict(heads=2, kv_heads=1, dim=8, vdim=40, window=16, s_heads=3, s_groups=1, s_norm_groups=1,
                                     s_state=8, s_vdim=24, s_conv=2, d_heads=3, d_kv=1, d_dim=24, d_vdim=8, d_conv=2, ff=0)),
+    "roomy_heads": dict(layers=("channel_delta", "parallel", "parallel", "delta"),
+                        sizes=dict(heads=4, kv_heads=1, dim=64, vdim=32, window=50, s_heads=2, s_groups=1, s_norm_groups=1,
+                                   s_state=64, s_vdim=32, s_conv=4, d_heads=2, d_kv=2, d_dim=32, d_vdim=64, d_conv=3, ff=72)),
     "wide_window": dict(layers=("parallel",), sizes=dict(heads=4, kv_heads=4, dim=16, vdim=16, window=300, s_heads=2, s_groups=2,
                                                         s_norm_groups=2, s_state=16, s_vdim=16, s_conv=5)),
 }
@@ -116,14 +119,22 @@ def test_layer_stream_matches_after_every_layer(tmp_path):
 
 
 # ---- schedules ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])             # bf16: tensor-core attention, bf16 pages and GEMM operands
 @pytest.mark.parametrize("shape", list(SHAPES))
-def test_prefill_decode_and_portions_agree_with_oracle(tmp_path, shape):
+def test_prefill_decode_and_portions_agree_with_oracle(tmp_path, shape, dtype):
     cfg, W = _model(shape)
     n = 330 if shape == "wide_window" else 90
     toks = _tokens(cfg, n, 5)
     want = O.forward(cfg, W, toks)
-    eng = _engine(tmp_path, cfg, W)
+    eng = _engine(tmp_path, cfg, W, dtype=dtype)
     whole = _run_alone(eng, toks, [n])
+    if dtype == "bf16":
+        assert _rel(whole, want) < BF16_TOL
+        for name, cuts in {"prefill_then_decode": [n - 40] + [1] * 40, "ragged": _cuts(n, [3, 37, 2, 16, 1, 17, 5])}.items():
+            got = _run_alone(eng, toks, cuts)
+            assert _rel(got, want) < BF16_TOL, name
+            assert _rel(got, whole) < BF16_TOL / 2, name      # different kernels for portions and single tokens: bf16 rounding
+        return
     assert _rel(whole, want) < F32_TOL
     schedules = {
         "by_token": [1] * n,
