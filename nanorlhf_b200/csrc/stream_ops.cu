@@ -20,72 +20,6 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// sum over the block; every thread gets the result.  red: >= 32 floats of shared memory.
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if (lane == 0) red[w] = v;
-  __syncthreads();
-  float t = 0.f;
-  for (int i = 0; i < nw; ++i) t += red[i];
-  return t;
-}
-
-template <typename WT>
-__global__ void embed_pos_kernel(const WT* __restrict__ embed, const WT* __restrict__ ptab, const int* __restrict__ tok,
-                                 const int* __restrict__ pos, float* __restrict__ out, int W) {
-  const long t = blockIdx.x;
-  const long a = static_cast<long>(tok[t]) * W, b = static_cast<long>(pos[t]) * W;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) out[t * W + c] = ld(embed, a + c) + ld(ptab, b + c);
-}
-
-template <typename HT>
-__global__ void stream_norm_kernel(float* __restrict__ results, long stride_r, int i, const float* __restrict__ o,
-                                   const float* __restrict__ xprev, const float* __restrict__ dw, const float* __restrict__ g,
-                                   float eps, float* __restrict__ xcur, HT* __restrict__ h, int W) {
-  __shared__ float red[32];
-  const long row = static_cast<long>(blockIdx.x) * W;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float last;
-    if (o != nullptr) {
-      last = xprev[row + c] + o[row + c];
-      results[i * stride_r + row + c] = last;
-    } else {
-      last = results[i * stride_r + row + c];
-    }
-    float x;
-    if (dw != nullptr) {
-      x = 0.f;
-      for (int j = 0; j < i; ++j) x += dw[j] * results[j * stride_r + row + c];
-      x += dw[i] * last;
-    } else {
-      x = last;
-    }
-    xcur[row + c] = x;
-    ss += x * x;
-  }
-  ss = block_sum(ss, red);
-  const float r = g[0] / sqrtf(ss / static_cast<float>(W) + eps);
-  for (int c = threadIdx.x; c < W; c += blockDim.x) st(h, row + c, xcur[row + c] * r);
-}
-
-template <typename OT>
-__global__ void act_cols_kernel(const float* __restrict__ in, long si, OT* __restrict__ out, long so, int act, long T, int C) {
-  const long n = T * C;
-  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
-    const long t = idx / C;
-    const int c = static_cast<int>(idx - t * C);
-    float v = in[t * si + c];
-    if (act == 1) {
-      v = fmaxf(v, 0.f);
-      v = v * v;
-    }
-    st(out, t * so + c, v);
-  }
-}
-
 __device__ __forceinline__ void st4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
 __device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
   const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
@@ -108,6 +42,92 @@ template <int V, typename OT>
 __device__ __forceinline__ void stv(OT* p, const float (&v)[V]) {
   if constexpr (V == 4) st4(p, v);
   else st(p, 0, v[0]);
+}
+
+// sum over the block; every thread gets the result.  red: >= 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+template <typename WT>
+__global__ void embed_pos_kernel(const WT* __restrict__ embed, const WT* __restrict__ ptab, const int* __restrict__ tok,
+                                 const int* __restrict__ pos, float* __restrict__ out, int W) {
+  const long t = blockIdx.x;
+  const long a = static_cast<long>(tok[t]) * W, b = static_cast<long>(pos[t]) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) out[t * W + c] = ld(embed, a + c) + ld(ptab, b + c);
+}
+
+template <typename HT, int V>        // V columns per thread and pass (4: 128-bit accesses, needs W % 4 == 0)
+__global__ void stream_norm_kernel(float* __restrict__ results, long stride_r, int i, const float* __restrict__ o,
+                                   const float* __restrict__ xprev, const float* __restrict__ dw, const float* __restrict__ g,
+                                   float eps, float* __restrict__ xcur, HT* __restrict__ h, int W) {
+  __shared__ float red[32];
+  const long row = static_cast<long>(blockIdx.x) * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float last[V], x[V];
+    if (o != nullptr) {
+      float a[V], b[V];
+      ldv<V>(xprev + row + c, a);
+      ldv<V>(o + row + c, b);
+#pragma unroll
+      for (int k = 0; k < V; ++k) last[k] = a[k] + b[k];
+      stv<V>(results + i * stride_r + row + c, last);
+    } else {
+      ldv<V>(results + i * stride_r + row + c, last);
+    }
+    if (dw != nullptr) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) x[k] = 0.f;
+      for (int j = 0; j < i; ++j) {
+        float r[V];
+        ldv<V>(results + j * stride_r + row + c, r);
+        const float wj = dw[j];
+#pragma unroll
+        for (int k = 0; k < V; ++k) x[k] += wj * r[k];
+      }
+      const float wi = dw[i];
+#pragma unroll
+      for (int k = 0; k < V; ++k) x[k] += wi * last[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) x[k] = last[k];
+    }
+    stv<V>(xcur + row + c, x);
+#pragma unroll
+    for (int k = 0; k < V; ++k) ss += x[k] * x[k];
+  }
+  ss = block_sum(ss, red);
+  const float r = g[0] / sqrtf(ss / static_cast<float>(W) + eps);
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float x[V];
+    ldv<V>(xcur + row + c, x);
+#pragma unroll
+    for (int k = 0; k < V; ++k) x[k] *= r;
+    stv<V>(h + row + c, x);
+  }
+}
+
+template <typename OT>
+__global__ void act_cols_kernel(const float* __restrict__ in, long si, OT* __restrict__ out, long so, int act, long T, int C) {
+  const long n = T * C;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < n; idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = idx / C;
+    const int c = static_cast<int>(idx - t * C);
+    float v = in[t * si + c];
+    if (act == 1) {
+      v = fmaxf(v, 0.f);
+      v = v * v;
+    }
+    st(out, t * so + c, v);
+  }
 }
 
 // four columns per thread: 128-bit loads, 64- / 128-bit stores
@@ -256,12 +276,19 @@ cudaError_t nrl_embed_pos(const void* embed, const void* pos_table, int w_f32, c
 cudaError_t nrl_stream_norm(float* results, long stride_r, int i, const float* o, const float* xprev, const float* dw,
                             const float* g, float eps, float* xcur, void* h, int h_f32, int T, int W, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
-  const int th = W >= 1024 ? 256 : 128;
-  if (h_f32)
-    stream_norm_kernel<float><<<T, th, 0, s>>>(results, stride_r, i, o, xprev, dw, g, eps, xcur, static_cast<float*>(h), W);
-  else
-    stream_norm_kernel<__nv_bfloat16><<<T, th, 0, s>>>(results, stride_r, i, o, xprev, dw, g, eps, xcur,
-                                                      static_cast<__nv_bfloat16*>(h), W);
+  const bool vec = W % 4 == 0 && stride_r % 4 == 0 && aligned(results, 16) && aligned(xcur, 16) && aligned(h, h_f32 ? 16 : 8) &&
+                   (o == nullptr || (aligned(o, 16) && aligned(xprev, 16)));
+  const int th = W >= 1024 * (vec ? 4 : 1) ? 256 : 128;
+#define NRL_SN(HT_, V_)                                                                                                            \
+  stream_norm_kernel<HT_, V_><<<T, th, 0, s>>>(results, stride_r, i, o, xprev, dw, g, eps, xcur, static_cast<HT_*>(h), W)
+  if (h_f32) {
+    if (vec) NRL_SN(float, 4);
+    else NRL_SN(float, 1);
+  } else {
+    if (vec) NRL_SN(__nv_bfloat16, 4);
+    else NRL_SN(__nv_bfloat16, 1);
+  }
+#undef NRL_SN
   return cudaGetLastError();
 }
 
