@@ -58,7 +58,7 @@ class LayerSpec:
 
 @dataclass
 class NezavikConfig:
-    vocab: int = 512
+    vocab: int = 256
     width: int = 128
     max_positions: int = 1024
     norm_eps: float = 1e-6
