@@ -532,3 +532,43 @@ def test_sampled_generation_shapes_and_eos(tmp_path):
     for row in a.tolist():
         if 5 in row:
             assert all(t == tok.pad_token_id for t in row[row.index(5) + 1:])
+
+
+# ---- the trace runner as a program ----------------------------------------------------------------------------------
+def test_trace_runner_replays_a_mixed_trace(tmp_path):
+    """bin/trace_run as a subprocess: five requests over four slots and a pool of 256 tokens, portions beside single tokens,
+    requests that pause, end and hand their pages and slots to later ones; the dumped logits against the oracle."""
+    import subprocess
+    import sys
+    import numpy as np
+    cfg, W = _model("roomy_heads", seed=9, width=48, vocab=131)
+    path = _save(tmp_path, cfg, W)
+    reqs = {name: _tokens(cfg, n, 90 + i) for i, (name, n) in enumerate([("a", 70), ("b", 9), ("c", 120), ("d", 33), ("e", 50)])}
+    steps = [
+        [("a", 0, 40, [39]), ("b", 0, 9, [0, 8])],
+        [("a", 40, 1, [0]), ("c", 0, 64, [])],
+        [("c", 64, 50, [49]), ("a", 41, 2, [0, 1]), ("d", 0, 17, [16])],
+        [("a", 43, 27, [26]), ("d", 17, 1, [0])],                       # b paused since step 0 and ends here
+        [("c", 114, 6, [0, 5]), ("d", 18, 15, [14])],
+        [("e", 0, 50, [0, 49])],                                        # takes a freed slot and freed pages
+    ]
+    ends = {3: ["b", "a"], 4: ["c", "d"], 5: ["e"]}
+    lines, wanted = [], {}
+    for i, st in enumerate(steps):
+        ent = [{"id": r, "tokens": reqs[r][lo:lo + n], "want": w} for r, lo, n, w in st]
+        lines.append(json.dumps({"step": i, "entries": ent, "end": ends.get(i, [])}))
+        wanted[i] = [(r, lo + j) for r, lo, n, w in st for j in w]
+    lines.insert(2, json.dumps({"step": "idle", "entries": [], "end": []}))
+    out = os.path.join(str(tmp_path), "out")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype, tol in (("float32", F32_TOL), ("bfloat16", BF16_TOL)):
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype, "--out", out,
+                            "--max-tokens", "256"], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        done = [l.split()[1] for l in r.stdout.splitlines() if l.startswith("done ")]
+        assert done == ["0", "1", "idle", "2", "3", "4", "5"]
+        full = {name: O.forward(cfg, W, toks) for name, toks in reqs.items()}
+        for i, rows in wanted.items():
+            got = torch.from_numpy(np.fromfile(os.path.join(out, f"{i}.f32"), dtype="<f4").reshape(len(rows), cfg["vocab"]).copy()).double()
+            want = torch.stack([full[r][p] for r, p in rows])
+            assert _rel(got, want) < tol, (dtype, i)
