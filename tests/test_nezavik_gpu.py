@@ -149,6 +149,17 @@ def test_prefill_decode_and_portions_agree_with_oracle(tmp_path, shape, dtype):
         assert _rel(got, whole) < 5e-5, name              # the cut must not matter beyond rounding
 
 
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_width_that_is_no_multiple_of_four(tmp_path, dtype):
+    cfg, W = _model("mixed", seed=3, width=42, vocab=53)
+    toks = _tokens(cfg, 60, 8)
+    want = O.forward(cfg, W, toks)
+    eng = _engine(tmp_path, cfg, W, dtype=dtype)
+    tol = F32_TOL if dtype == "fp32" else BF16_TOL
+    assert _rel(_run_alone(eng, toks, [60]), want) < tol
+    assert _rel(_run_alone(eng, toks, [25, 3] + [1] * 32), want) < tol
+
+
 def test_long_decode(tmp_path):
     cfg, W = _model("mixed")
     toks = _tokens(cfg, 260, 6)
@@ -285,7 +296,7 @@ def test_needle_just_inside_and_outside_the_window(tmp_path, window, dtype):
 
 
 @pytest.mark.parametrize("D,Dv,Hq,Hkv,window", [(128, 128, 8, 2, 100), (24, 16, 6, 3, 11), (64, 32, 4, 4, 40), (40, 72, 3, 1, 33),
-                                                (16, 16, 5, 1, 17), (32, 128, 2, 1, 64)])
+                                                (16, 16, 5, 1, 17), (32, 128, 2, 1, 64), (16, 16, 34, 2, 20), (12, 10, 4, 2, 9)])
 @pytest.mark.parametrize("step", ["portions", "single_tokens"])
 def test_window_attention_kernels_against_plain_softmax(D, Dv, Hq, Hkv, window, step):
     """Every window-attention kernel on random bf16 pages, entries of unequal length with and without earlier context, against
@@ -331,7 +342,7 @@ def test_window_attention_kernels_against_plain_softmax(D, Dv, Hq, Hkv, window, 
         assert err < 2e-2, (impl, err)
 
 
-@pytest.mark.parametrize("part,nparts", [(12, 5), (64, 2), (256, 3), (300, 1), (1024, 2)])
+@pytest.mark.parametrize("part,nparts", [(12, 5), (10, 3), (64, 2), (256, 3), (300, 1), (1024, 2), (257, 2)])
 @pytest.mark.parametrize("gate_act,gate_first", [("silu", True), ("sigmoid", False)])
 def test_gated_part_rmsnorm_narrow_and_wide_parts(part, nparts, gate_act, gate_first):
     from nanorlhf_b200.ops import hybrid as hy, native
