@@ -25,6 +25,43 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// first key a query at position p sees
+__device__ __forceinline__ int first_key(int p, int window, int chunked) {
+  if (chunked) return p - p % window;
+  return p - window + 1 > 0 ? p - window + 1 : 0;
+}
+__device__ __forceinline__ float sigmoid_(float z) { return 1.f / (1.f + expf(-z)); }
+
+// warp per (token, key/value head): keys and (optionally blended) values into the pages
+template <typename CT>
+__global__ void kv_write_blend_kernel(const float* __restrict__ k, long sk, float* __restrict__ v, long sv, const float* __restrict__ v_other,
+                                      long svo, const float* __restrict__ lambda, CT* __restrict__ k_cache, CT* __restrict__ v_cache,
+                                      const int* __restrict__ kv_slot, long T, int Hkv, int D, int Dv, int page) {
+  const long wid = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= T * Hkv) return;
+  const long t = wid / Hkv;
+  const int g = static_cast<int>(wid - t * Hkv);
+  const int slot = kv_slot[t];
+  const long pg = slot / page, off = slot % page;
+  const float* kr = k + t * sk + static_cast<long>(g) * D;
+  CT* kd = k_cache + ((pg * Hkv + g) * page + off) * D;
+  for (int c = lane; c < D; c += 32) st(kd, c, kr[c]);
+  float* vr = v + t * sv + static_cast<long>(g) * Dv;
+  CT* vd = v_cache + ((pg * Hkv + g) * page + off) * Dv;
+  if (v_other != nullptr) {
+    const float lam = lambda[0];
+    const float* vo = v_other + t * svo + static_cast<long>(g) * Dv;
+    for (int c = lane; c < Dv; c += 32) {
+      const float x = (1.f - lam) * vr[c] + lam * vo[c];
+      vr[c] = x;
+      st(vd, c, x);
+    }
+  } else {
+    for (int c = lane; c < Dv; c += 32) st(vd, c, vr[c]);
+  }
+}
+
 // warp per (token, head): heads 0..Hq-1 are queries (normalised in place), Hq..Hq+Hkv-1 keys (normalised into the cache),
 // then Hkv value heads (copied into the cache)
 template <typename CT>
@@ -72,7 +109,8 @@ template <typename CT, typename OT>
 __global__ void window_attention_kernel(const float* __restrict__ q, long sq, const CT* __restrict__ k_cache,
                                         const CT* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                                         const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale,
-                                        float out_scale, OT* __restrict__ out, long so, int Hq, int Hkv, int D, int Dv, int page) {
+                                        float out_scale, OT* __restrict__ out, long so, int Hq, int Hkv, int D, int Dv, int page,
+                                        NrlAttnMods md) {
   extern __shared__ float sm[];
   float* sq_ = sm;                               // [D]
   float* accs = sq_ + D;                         // [kWarps][Dv]
@@ -84,8 +122,11 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
   const int* bt = block_table + static_cast<long>(tok_entry[t]) * max_blocks;
   for (int c = threadIdx.x; c < D; c += blockDim.x) sq_[c] = q[t * sq + static_cast<long>(h) * D + c];
   __syncthreads();
-  const int lo = p - window + 1 > 0 ? p - window + 1 : 0;
+  const int lo = first_key(p, window, md.chunked);
   const int nkeys = p - lo + 1;
+  if (md.head_scale != nullptr) scale *= md.head_scale[h];
+  const float slope = md.head_slope != nullptr ? md.head_slope[h] : 0.f;
+  if (md.gate != nullptr) out_scale *= sigmoid_(md.gate[t * md.gate_stride + h]);
   float m = -INFINITY, l = 0.f;
   float acc[kMaxDvPerLane];
 #pragma unroll
@@ -101,7 +142,7 @@ __global__ void window_attention_kernel(const float* __restrict__ q, long sq, co
       const CT* kr = k_cache + cell * D;
       float d = 0.f;
       for (int c = 0; c < D; ++c) d += sq_[c] * ld(kr, c);
-      sc = d * scale;
+      sc = d * scale - slope * static_cast<float>(p - j);
       vrow = cell * Dv;
     }
     const float mn = fmaxf(m, warp_max(sc));
@@ -183,7 +224,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_entry,
                              const int* __restrict__ pos, int window, float scale, float out_scale, OT* __restrict__ out, long so,
-                             int T, int Hq, int Hkv, int D, int Dv, int page, int HB, int QT) {
+                             int T, int Hq, int Hkv, int D, int Dv, int page, int HB, int QT, NrlAttnMods md) {
   extern __shared__ float sm[];
   float* qs = sm;                                  // [NQ][D], scaled
   float* ps = qs + NQ * D;                         // [kWarps][32][NQ]
@@ -203,20 +244,25 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
     while (tn < t_end && tok_entry[tn] == e) ++tn;
     const int nt = tn - t, nqs = nt * hb;
     const int p_first = pos[t];
-    const int lo = p_first - window + 1 > 0 ? p_first - window + 1 : 0;
+    const int lo = first_key(p_first, window, md.chunked);       // the first key of a run's first token: later tokens start no earlier
     const int nkeys = p_first + nt - lo;
     const int* bt = block_table + static_cast<long>(e) * max_blocks;
     __syncthreads();
     for (int idx = threadIdx.x; idx < NQ * D; idx += blockDim.x) {
       const int qi = idx / D, c = idx - qi * D;
       float v = 0.f;
-      if (qi < nqs) v = q[static_cast<long>(t + qi / hb) * sq + static_cast<long>(h0 + qi % hb) * D + c] * scale;
+      if (qi < nqs) {
+        const int hq = h0 + qi % hb;
+        v = q[static_cast<long>(t + qi / hb) * sq + static_cast<long>(hq) * D + c] * scale;
+        if (md.head_scale != nullptr) v *= md.head_scale[hq];
+      }
       qs[idx] = v;
     }
     __syncthreads();
-    float m[NQ], l[NQ], acc[NQ][4];
+    float m[NQ], l[NQ], acc[NQ][4], slope[NQ];
 #pragma unroll
     for (int i = 0; i < NQ; ++i) {
+      slope[i] = (md.head_slope != nullptr && i < nqs) ? md.head_slope[h0 + i % hb] : 0.f;
       m[i] = -INFINITY;
       l[i] = 0.f;
       acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -252,8 +298,8 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
 #pragma unroll
       for (int i = 0; i < NQ; ++i) {
         const int pq = p_first + i / hb;                                   // position of query i
-        const bool valid = ok && i < nqs && j <= pq && j > pq - window;
-        const float sc = valid ? s[i] : -INFINITY;
+        const bool valid = ok && i < nqs && j <= pq && j >= first_key(pq, window, md.chunked);
+        const float sc = valid ? s[i] - slope[i] * static_cast<float>(pq - j) : -INFINITY;
         const float mn = fmaxf(m[i], warp_max(sc));
         float pr = 0.f;
         if (mn != -INFINITY) {                                              // some key of this query has been seen
@@ -304,7 +350,9 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
         lt += f * rml[(x * NQ + qi) * 2 + 1];
         a += f * racc[(static_cast<long>(x) * NQ + qi) * Dv + c];
       }
-      st(out, static_cast<long>(t + qi / hb) * so + static_cast<long>(h0 + qi % hb) * Dv + c, out_scale * (a / lt));
+      float os = out_scale;
+      if (md.gate != nullptr) os *= sigmoid_(md.gate[static_cast<long>(t + qi / hb) * md.gate_stride + h0 + qi % hb]);
+      st(out, static_cast<long>(t + qi / hb) * so + static_cast<long>(h0 + qi % hb) * Dv + c, os * (a / lt));
     }
     t = tn;
   }
@@ -313,7 +361,7 @@ window_attention_tile_kernel(const float* __restrict__ q, long sq, const CT* __r
 template <typename CT, typename OT, int NQ>
 cudaError_t launch_tile(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                         const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T,
-                        int Hq, int Hkv, int D, int Dv, int page, cudaStream_t s) {
+                        int Hq, int Hkv, int D, int Dv, int page, const NrlAttnMods& md, cudaStream_t s) {
   const int per_g = Hq / Hkv;
   const int HB = per_g < NQ ? per_g : NQ, QT = NQ / HB > 1 ? NQ / HB : 1;
   const size_t smem = sizeof(float) * (static_cast<size_t>(NQ) * D + kWarps * 32 * NQ + static_cast<size_t>(kWarps) * NQ * Dv + kWarps * NQ * 2);
@@ -327,16 +375,16 @@ cudaError_t launch_tile(const float* q, long sq, const void* k_cache, const void
   }
   const dim3 grid((T + QT - 1) / QT, Hkv, (per_g + HB - 1) / HB);
   kern<<<grid, kWarps * 32, smem, s>>>(q, sq, static_cast<const CT*>(k_cache), static_cast<const CT*>(v_cache), block_table, max_blocks,
-                                       tok_entry, pos, window, scale, out_scale, static_cast<OT*>(out), so, T, Hq, Hkv, D, Dv, page, HB, QT);
+                                       tok_entry, pos, window, scale, out_scale, static_cast<OT*>(out), so, T, Hq, Hkv, D, Dv, page, HB, QT, md);
   return cudaGetLastError();
 }
 
 template <typename CT, typename OT>
 cudaError_t launch_tile_nq(int nq, const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                            int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out,
-                           long so, int T, int Hq, int Hkv, int D, int Dv, int page, cudaStream_t s) {
+                           long so, int T, int Hq, int Hkv, int D, int Dv, int page, const NrlAttnMods& md, cudaStream_t s) {
 #define NRL_WA(NQ_) return launch_tile<CT, OT, NQ_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, \
-                                                     out_scale, out, so, T, Hq, Hkv, D, Dv, page, s)
+                                                     out_scale, out, so, T, Hq, Hkv, D, Dv, page, md, s)
   if (nq <= 2) NRL_WA(2);
   if (nq <= 4) NRL_WA(4);
   if (nq <= 8) NRL_WA(8);
@@ -364,14 +412,33 @@ cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, cons
   return cudaGetLastError();
 }
 
+cudaError_t nrl_kv_write_blend(const float* k, long sk, float* v, long sv, const float* v_other, long svo, const float* lambda,
+                               void* k_cache, void* v_cache, int cache_f32, const int* kv_slot, int T, int Hkv, int D, int Dv, int page,
+                               cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (v_other != nullptr && lambda == nullptr) return cudaErrorInvalidValue;
+  const long warps = static_cast<long>(T) * Hkv;
+  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+  if (cache_f32)
+    kv_write_blend_kernel<float><<<blocks, 128, 0, s>>>(k, sk, v, sv, v_other, svo, lambda, static_cast<float*>(k_cache),
+                                                        static_cast<float*>(v_cache), kv_slot, T, Hkv, D, Dv, page);
+  else
+    kv_write_blend_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(k, sk, v, sv, v_other, svo, lambda, static_cast<__nv_bfloat16*>(k_cache),
+                                                                static_cast<__nv_bfloat16*>(v_cache), kv_slot, T, Hkv, D, Dv, page);
+  return cudaGetLastError();
+}
+
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D, int Dv,
-                                 int page, int single_token, int impl, int nsplit, float* part, cudaStream_t s) {
+                                 int page, int single_token, int impl, int nsplit, float* part, const NrlAttnMods* mods, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
   if (Dv > 32 * kMaxDvPerLane || Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
+  NrlAttnMods md = {0, nullptr, nullptr, nullptr, 0};
+  if (mods != nullptr) md = *mods;
+  const bool plain = !md.chunked && md.head_scale == nullptr && md.head_slope == nullptr && md.gate == nullptr;
   // prompt portions over bf16 pages: tensor cores
-  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page)) {
+  if (plain && (impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page)) {
     if (single_token && nsplit >= 1 && part != nullptr)
       return nrl_window_attention_decode(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out,
                                          so, T, Hq, Hkv, D, Dv, page, nsplit, part, s);
@@ -383,9 +450,9 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
     // queries per block: the heads of one key/value head for single-token steps, 16 (tokens x heads) when entries hold runs
     const int nq = single_token ? Hq / Hkv : 16;
     return cache_f32 ? launch_tile_nq<float, float>(nq, q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale,
-                                                    out_scale, out, so, T, Hq, Hkv, D, Dv, page, s)
+                                                    out_scale, out, so, T, Hq, Hkv, D, Dv, page, md, s)
                      : launch_tile_nq<__nv_bfloat16, __nv_bfloat16>(nq, q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos,
-                                                                    window, scale, out_scale, out, so, T, Hq, Hkv, D, Dv, page, s);
+                                                                    window, scale, out_scale, out, so, T, Hq, Hkv, D, Dv, page, md, s);
   }
   const size_t smem = sizeof(float) * (D + kWarps * Dv + 2 * kWarps);
   if (smem > 48 * 1024) return cudaErrorInvalidValue;
@@ -393,11 +460,11 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
   if (cache_f32)
     window_attention_kernel<float, float><<<grid, kWarps * 32, smem, s>>>(
         q, sq, static_cast<const float*>(k_cache), static_cast<const float*>(v_cache), block_table, max_blocks, tok_entry, pos, window,
-        scale, out_scale, static_cast<float*>(out), so, Hq, Hkv, D, Dv, page);
+        scale, out_scale, static_cast<float*>(out), so, Hq, Hkv, D, Dv, page, md);
   else
     window_attention_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kWarps * 32, smem, s>>>(
         q, sq, static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks,
-        tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so, Hq, Hkv, D, Dv, page);
+        tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so, Hq, Hkv, D, Dv, page, md);
   return cudaGetLastError();
 }
 

@@ -81,7 +81,8 @@ void gated_part_rmsnorm(const Tensor& y, const Tensor& gate, const Tensor& w, in
 }
 
 void causal_conv(const Tensor& in, const Tensor& w, const c10::optional<Tensor>& bias, Tensor state, Tensor out, const Tensor& cu,
-                 const Tensor& tok_entry, const Tensor& start, const Tensor& state_slot) {
+                 const Tensor& tok_entry, const Tensor& start, const Tensor& state_slot, const c10::optional<Tensor>& in_bias,
+                 int64_t act) {
   c10::cuda::CUDAGuard guard(out.device());
   const int T = static_cast<int>(in.size(0)), C = static_cast<int>(in.size(1)), taps = static_cast<int>(w.size(1));
   const int E = static_cast<int>(start.numel());
@@ -90,11 +91,14 @@ void causal_conv(const Tensor& in, const Tensor& w, const c10::optional<Tensor>&
   TORCH_CHECK(state.is_contiguous() && state.dim() == 3 && state.size(1) == taps - 1 && state.size(2) == C, "causal_conv: state [slots, taps-1, C]");
   TORCH_CHECK(cu.numel() == E + 1 && tok_entry.numel() >= T && state_slot.numel() == E, "causal_conv: plan");
   if (bias.has_value()) TORCH_CHECK(bias->numel() == C, "causal_conv: bias");
-  check(nrl_causal_conv(f32(in, "in"), in.stride(0), f32(w, "w"), bias.has_value() ? f32(*bias, "bias") : nullptr, f32(state, "state"),
+  if (in_bias.has_value()) TORCH_CHECK(in_bias->numel() == C, "causal_conv: in_bias");
+  const float* ib = in_bias.has_value() ? f32(*in_bias, "in_bias") : nullptr;
+  check(nrl_causal_conv(f32(in, "in"), in.stride(0), ib, static_cast<int>(act), f32(w, "w"),
+                        bias.has_value() ? f32(*bias, "bias") : nullptr, f32(state, "state"),
                         f32w(out, "out"), out.stride(0), i32(cu, "cu"), i32(tok_entry, "tok_entry"), i32(start, "start"),
                         i32(state_slot, "state_slot"), T, E, C, taps, cur_stream()),
         "causal_conv");
-  check(nrl_causal_conv_carry(f32(in, "in"), in.stride(0), f32w(state, "state"), i32(cu, "cu"), i32(start, "start"),
+  check(nrl_causal_conv_carry(f32(in, "in"), in.stride(0), ib, f32w(state, "state"), i32(cu, "cu"), i32(start, "start"),
                               i32(state_slot, "state_slot"), E, C, taps, cur_stream()),
         "causal_conv_carry");
 }
@@ -164,7 +168,9 @@ void qknorm_kv_write(Tensor q, const Tensor& k, const Tensor& v, const Tensor& q
 }
 
 void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table, const Tensor& tok_entry,
-                      const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out, int64_t impl) {
+                      const Tensor& pos, int64_t window, double scale, double out_scale, Tensor out, int64_t impl, bool chunked,
+                      const c10::optional<Tensor>& head_scale, const c10::optional<Tensor>& head_slope,
+                      const c10::optional<Tensor>& gate) {
   const bool single_token = block_table.size(0) == q.size(0);
   c10::cuda::CUDAGuard guard(q.device());
   const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
@@ -172,10 +178,25 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   const int T = static_cast<int>(q.size(0)), Hq = static_cast<int>(q.size(1) / D);
   TORCH_CHECK(block_table.dim() == 2 && out.dim() == 2 && out.size(0) == T && out.size(1) == static_cast<int64_t>(Hq) * Dv,
               "window_attention: shapes");
+  NrlAttnMods md = {chunked ? 1 : 0, nullptr, nullptr, nullptr, 0};
+  if (head_scale.has_value()) {
+    TORCH_CHECK(head_scale->numel() == Hq && head_scale->is_contiguous(), "window_attention: head_scale [Hq]");
+    md.head_scale = f32(*head_scale, "head_scale");
+  }
+  if (head_slope.has_value()) {
+    TORCH_CHECK(head_slope->numel() == Hq && head_slope->is_contiguous(), "window_attention: head_slope [Hq]");
+    md.head_slope = f32(*head_slope, "head_slope");
+  }
+  if (gate.has_value()) {
+    TORCH_CHECK(gate->dim() == 2 && gate->size(0) == T && gate->size(1) == Hq, "window_attention: gate [T, Hq]");
+    md.gate = f32(*gate, "gate");
+    md.gate_stride = gate->stride(0);
+  }
+  const bool plain = !chunked && md.head_scale == nullptr && md.head_slope == nullptr && md.gate == nullptr;
   // steps of single tokens on bf16 pages: cut the key walk into parts so that few sequences still fill the GPU
   int nsplit = 0;
   Tensor part;
-  if (single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
+  if (plain && single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
       nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page)) {
     nsplit = nrl_window_attention_splits(T, Hq, Hkv, static_cast<int>(window), static_cast<int>(block_table.size(1)), page);
     if (nsplit >= 1) part = at::empty({T, Hq, 4 * nsplit, Dv + 2}, q.options().dtype(at::kFloat));
@@ -184,8 +205,88 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
                              i32(block_table, "block_table"), static_cast<int>(block_table.size(1)), i32(tok_entry, "tok_entry"),
                              i32(pos, "pos"), static_cast<int>(window), static_cast<float>(scale), static_cast<float>(out_scale),
                              out.data_ptr(), out.stride(0), typed(out, "out"), T, Hq, Hkv, D, Dv, page, single_token ? 1 : 0, static_cast<int>(impl),
-                             nsplit, nsplit >= 1 ? part.data_ptr<float>() : nullptr, cur_stream()),
+                             nsplit, nsplit >= 1 ? part.data_ptr<float>() : nullptr, &md, cur_stream()),
         "window_attention");
+}
+
+void kv_write_blend(const Tensor& k, Tensor v, const c10::optional<Tensor>& v_other, const c10::optional<Tensor>& lambda, Tensor k_cache,
+                    Tensor v_cache, const Tensor& kv_slot) {
+  c10::cuda::CUDAGuard guard(k.device());
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "kv_write_blend: caches");
+  const int Hkv = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
+  const int Dv = static_cast<int>(v_cache.size(3));
+  const int T = static_cast<int>(k.size(0));
+  TORCH_CHECK(k.dim() == 2 && v.dim() == 2 && v.size(0) == T && k.size(1) == static_cast<int64_t>(Hkv) * D &&
+                  v.size(1) == static_cast<int64_t>(Hkv) * Dv && kv_slot.numel() >= T, "kv_write_blend: shapes");
+  TORCH_CHECK(v_other.has_value() == lambda.has_value(), "kv_write_blend: v_other and lambda go together");
+  if (v_other.has_value())
+    TORCH_CHECK(v_other->dim() == 2 && v_other->size(0) == T && v_other->size(1) == v.size(1) && lambda->numel() == 1,
+                "kv_write_blend: v_other like v, lambda one number");
+  const int cf = typed(k_cache, "k_cache");
+  TORCH_CHECK(typed(v_cache, "v_cache") == cf, "kv_write_blend: cache types differ");
+  check(nrl_kv_write_blend(f32(k, "k"), k.stride(0), f32w(v, "v"), v.stride(0), v_other.has_value() ? f32(*v_other, "v_other") : nullptr,
+                           v_other.has_value() ? v_other->stride(0) : 0, lambda.has_value() ? f32(*lambda, "lambda") : nullptr,
+                           k_cache.data_ptr(), v_cache.data_ptr(), cf, i32(kv_slot, "kv_slot"), T, Hkv, D, Dv, page, cur_stream()),
+        "kv_write_blend");
+}
+
+void embed_hashed(const Tensor& embed, const c10::optional<Tensor>& pair, const Tensor& tok, const Tensor& cu, const Tensor& tok_entry,
+                  const Tensor& start, const Tensor& state_slot, const c10::optional<Tensor>& prev_state, double scale, int64_t mul_prev,
+                  int64_t mul_cur, int64_t buckets, Tensor out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  const int wf = typed(embed, "embed");
+  const int T = static_cast<int>(tok.numel()), W = static_cast<int>(embed.size(1)), E = static_cast<int>(start.numel());
+  TORCH_CHECK(embed.is_contiguous() && out.is_contiguous() && out.size(0) >= T && out.size(1) == W, "embed_hashed: shapes");
+  TORCH_CHECK(pair.has_value() == prev_state.has_value(), "embed_hashed: the pair table needs the per-slot previous tokens");
+  if (pair.has_value()) {
+    TORCH_CHECK(typed(*pair, "pair") == wf && pair->is_contiguous() && pair->size(1) == W && pair->size(0) == buckets + 1 && buckets > 0,
+                "embed_hashed: pair table [buckets + 1, W]");
+    TORCH_CHECK(prev_state->scalar_type() == torch::kInt32 && prev_state->is_contiguous(), "embed_hashed: prev_state int32 [slots]");
+  }
+  check(nrl_embed_hashed(embed.data_ptr(), pair.has_value() ? pair->data_ptr() : nullptr, wf, i32(tok, "tok"), i32(cu, "cu"),
+                         i32(tok_entry, "tok_entry"), i32(start, "start"), i32(state_slot, "state_slot"),
+                         prev_state.has_value() ? prev_state->data_ptr<int>() : nullptr, static_cast<float>(scale), mul_prev, mul_cur,
+                         buckets, f32w(out, "out"), T, E, W, cur_stream()),
+        "embed_hashed");
+}
+
+void group_norm_residual(Tensor x, const c10::optional<Tensor>& o, const c10::optional<Tensor>& gate, const c10::optional<Tensor>& gate_bias,
+                         const c10::optional<Tensor>& w_post, const c10::optional<Tensor>& w_pre, int64_t groups, double eps,
+                         const c10::optional<Tensor>& h) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), "group_norm_residual: x [T, W] contiguous");
+  const int T = static_cast<int>(x.size(0)), W = static_cast<int>(x.size(1));
+  if (o.has_value()) TORCH_CHECK(o->is_contiguous() && o->size(0) == T && o->size(1) == W && w_post.has_value() && w_post->numel() == W, "group_norm_residual: o / w_post");
+  if (gate.has_value()) TORCH_CHECK(gate->dim() == 2 && gate->size(0) == T && gate->size(1) == W, "group_norm_residual: gate [T, W]");
+  if (gate_bias.has_value()) TORCH_CHECK(gate_bias->numel() == W, "group_norm_residual: gate_bias [W]");
+  if (h.has_value()) TORCH_CHECK(h->is_contiguous() && h->size(0) == T && h->size(1) == W && w_pre.has_value() && w_pre->numel() == W, "group_norm_residual: h / w_pre");
+  check(nrl_group_norm_residual(f32w(x, "x"), o.has_value() ? f32(*o, "o") : nullptr, gate.has_value() ? f32(*gate, "gate") : nullptr,
+                                gate.has_value() ? gate->stride(0) : 0, gate_bias.has_value() ? f32(*gate_bias, "gate_bias") : nullptr,
+                                w_post.has_value() ? f32(*w_post, "w_post") : nullptr, w_pre.has_value() ? f32(*w_pre, "w_pre") : nullptr,
+                                static_cast<int>(groups), static_cast<float>(eps), h.has_value() ? h->data_ptr() : nullptr,
+                                h.has_value() ? typed(*h, "h") : 1, T, W, cur_stream()),
+        "group_norm_residual");
+}
+
+void moe_route(const Tensor& router, const c10::optional<Tensor>& router_bias, int64_t top, const c10::optional<Tensor>& gu, int64_t ff,
+               const c10::optional<Tensor>& act, const c10::optional<Tensor>& ids, const c10::optional<Tensor>& wts) {
+  c10::cuda::CUDAGuard guard(router.device());
+  TORCH_CHECK(router.dim() == 2, "moe_route: router [T, E]");
+  const int T = static_cast<int>(router.size(0)), E = static_cast<int>(router.size(1));
+  if (router_bias.has_value()) TORCH_CHECK(router_bias->numel() == E, "moe_route: router_bias [E]");
+  TORCH_CHECK(act.has_value() == gu.has_value(), "moe_route: gu and act go together");
+  if (act.has_value())
+    TORCH_CHECK(gu->dim() == 2 && gu->size(0) == T && gu->size(1) == static_cast<int64_t>(E) * 2 * ff && act->dim() == 2 &&
+                    act->size(0) == T && act->size(1) == static_cast<int64_t>(E) * ff, "moe_route: gu [T, E*2ff], act [T, E*ff]");
+  if (ids.has_value()) TORCH_CHECK(ids->scalar_type() == torch::kInt32 && ids->is_contiguous() && ids->numel() == static_cast<int64_t>(T) * top, "moe_route: ids int32 [T, top]");
+  if (wts.has_value()) TORCH_CHECK(ids.has_value() && wts->is_contiguous() && wts->numel() == static_cast<int64_t>(T) * top, "moe_route: wts float [T, top]");
+  Tensor wt = wts.has_value() ? *wts : Tensor();
+  check(nrl_moe_route(f32(router, "router"), router.stride(0), router_bias.has_value() ? f32(*router_bias, "router_bias") : nullptr, E,
+                      static_cast<int>(top), gu.has_value() ? f32(*gu, "gu") : nullptr, gu.has_value() ? gu->stride(0) : 0,
+                      static_cast<int>(ff), act.has_value() ? act->data_ptr() : nullptr, act.has_value() ? act->stride(0) : 0,
+                      act.has_value() ? typed(*act, "act") : 1, ids.has_value() ? ids->data_ptr<int>() : nullptr,
+                      wts.has_value() ? f32w(wt, "wts") : nullptr, T, cur_stream()),
+        "moe_route");
 }
 
 }  // namespace
@@ -196,13 +297,22 @@ void bind_hybrid(pybind11::module_& m) {
   m.def("stream_norm", &stream_norm, "close a layer, form the depth-weighted stream and its single-gain RMS norm");
   m.def("act_cols", &act_cols, "typed out = act(float in): 0 copy, 1 relu^2");
   m.def("gated_part_rmsnorm", &gated_part_rmsnorm, "part-wise RMS norm with a silu / sigmoid gate before or after it");
-  m.def("causal_conv", &causal_conv, "depthwise causal convolution + silu with taps carried per state slot");
+  m.def("causal_conv", &causal_conv, "depthwise causal convolution (+ silu) with taps carried per state slot", pybind11::arg("in"),
+        pybind11::arg("w"), pybind11::arg("bias"), pybind11::arg("state"), pybind11::arg("out"), pybind11::arg("cu"),
+        pybind11::arg("tok_entry"), pybind11::arg("start"), pybind11::arg("state_slot"), pybind11::arg("in_bias") = pybind11::none(),
+        pybind11::arg("act") = 1);
   m.def("ssd_scan", &ssd_scan, "state-space scan with a scalar decay per head, state carried per slot");
   m.def("delta_prep", &delta_prep, "unit q / k, beta and decays of the gated delta rule");
   m.def("delta_scan", &delta_scan, "gated delta rule scan, state carried per slot");
   m.def("qknorm_kv_write", &qknorm_kv_write, "per-head RMS norm of q (in place) and k (into the paged cache), v into the cache");
   m.def("window_attention", &window_attention, "sliding-window attention over the paged cache", pybind11::arg("q"),
         pybind11::arg("k_cache"), pybind11::arg("v_cache"), pybind11::arg("block_table"), pybind11::arg("tok_entry"), pybind11::arg("pos"),
-        pybind11::arg("window"), pybind11::arg("scale"), pybind11::arg("out_scale"), pybind11::arg("out"), pybind11::arg("impl") = 0);
+        pybind11::arg("window"), pybind11::arg("scale"), pybind11::arg("out_scale"), pybind11::arg("out"), pybind11::arg("impl") = 0,
+        pybind11::arg("chunked") = false, pybind11::arg("head_scale") = pybind11::none(), pybind11::arg("head_slope") = pybind11::none(),
+        pybind11::arg("gate") = pybind11::none());
+  m.def("kv_write_blend", &kv_write_blend, "keys and (optionally blended) values of a step's tokens into their pages");
+  m.def("embed_hashed", &embed_hashed, "x0 = embed[tok] * scale + pair[hash(previous token, token)] (float), previous tokens carried per slot");
+  m.def("group_norm_residual", &group_norm_residual, "x += groupnorm(o * sigmoid(gate)) * w_post; h = groupnorm(x) * w_pre");
+  m.def("moe_route", &moe_route, "top-k routing with softmax over the chosen logits; dense-form expert activations");
 }
 }  // namespace nrl

@@ -11,10 +11,42 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Optional terms of the paged attention kernels: the mask's form, per-head score terms and a per-head output gate.
+typedef struct {
+  int chunked;               // 0: sliding window, key j seen from position p when p - window < j <= p
+                             // 1: chunks of `window` positions counted from position 0: floor(j / window) == floor(p / window), j <= p
+  const float* head_scale;   // [Hq] or null: the score multiplier of head h is scale * head_scale[h]
+  const float* head_slope;   // [Hq] or null: head_slope[h] * (p - j) is taken off the score
+  const float* gate;         // [T, Hq] float (row stride gate_stride) or null: head h's output is multiplied by sigmoid(gate[t, h])
+  long gate_stride;
+} NrlAttnMods;
+
 extern "C" {
 // x0[t] = table[tok[t]] + pos_table[pos[t]]  (float out)
 cudaError_t nrl_embed_pos(const void* embed, const void* pos_table, int w_f32, const int* tok, const int* pos, float* out,
                           int T, int W, cudaStream_t s);
+
+// x0[t] = embed[tok[t]] * scale + pair[row] (float out): a hashed row per (previous token, token) pair,
+//   row = (prev * mul_prev + tok * mul_cur) mod buckets, row `buckets` for the first token of a sequence; pair == nullptr: no
+// such term.  The previous token of an entry's first token is read from prev_state[state_slot] (int [slots]); a second launch
+// stores every entry's last token there.
+cudaError_t nrl_embed_hashed(const void* embed, const void* pair, int w_f32, const int* tok, const int* cu, const int* tok_entry,
+                             const int* start, const int* state_slot, int* prev_state, float scale, long mul_prev, long mul_cur,
+                             long buckets, float* out, int T, int E, int W, cudaStream_t s);
+
+// Sublayer boundary of a stream with a norm before and after every sublayer and a gated residual; norms are RMS norms over
+// `groups` equal consecutive parts of the vector with a weight per column.
+//   if (o)  y = o * sigmoid(gate + gate_bias)   (gate float, row stride sg, null: y = o);   x += y / rms_part(y) * w_post
+//   if (h)  h (typed) = x / rms_part(x) * w_pre
+cudaError_t nrl_group_norm_residual(float* x, const float* o, const float* gate, long sg, const float* gate_bias, const float* w_post,
+                                    const float* w_pre, int groups, float eps, void* h, int h_f32, int T, int W, cudaStream_t s);
+
+// Mixture-of-experts routing.  router float [T, E] (row stride sr) + router_bias [E]; the `top` largest logits (ties: lowest
+// index) are chosen, weights = softmax over the chosen logits.  ids int [T, top], wts float [T, top] (either may be null).
+// Dense form (act != nullptr): gu float (row stride sgu) holds per expert ff gate columns then ff up columns;
+//   act[t, e*ff + c] (typed, row stride sa) = weight_e * silu(gate) * up, 0 for experts that were not chosen.
+cudaError_t nrl_moe_route(const float* router, long sr, const float* router_bias, int E, int top, const float* gu, long sgu, int ff,
+                          void* act, long sa, int act_f32, int* ids, float* wts, int T, cudaStream_t s);
 
 // Layer boundary of a depth-weighted residual stream.  results: float [n_results_cap, stride_r] with rows of W.
 //   if (o)  results[i] = xprev + o                      (closes the previous layer)
@@ -33,14 +65,16 @@ cudaError_t nrl_gated_part_rmsnorm(const float* y, long sy, const float* gate, l
                                    int gate_act, int gate_first, float eps, float scale, void* out, long so, int out_f32,
                                    int T, int n, cudaStream_t s);
 
-// Depthwise causal convolution over time with carried taps, then silu.  in float [T, C] (row stride si), w float [C, taps],
-// bias float [C] or null, state float [slots, taps-1, C] (oldest first).  out float [T, C] (row stride so).
+// Depthwise causal convolution over time with carried taps.  in float [T, C] (row stride si) plus in_bias float [C] or null
+// (a bias of the projection that produced `in`: it is part of the convolution's input and of the carried taps, while the
+// time before a sequence's start is zero), w float [C, taps], bias float [C] or null (added after the convolution),
+// state float [slots, taps-1, C] (oldest first).  out float [T, C] (row stride so) = act ? silu(y) : y.
 // nrl_causal_conv reads the old state; nrl_causal_conv_carry (launched after it) stores the step's last taps-1 inputs.
-cudaError_t nrl_causal_conv(const float* in, long si, const float* w, const float* bias, const float* state, float* out, long so,
-                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int E, int C,
-                            int taps, cudaStream_t s);
-cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const int* cu, const int* start, const int* state_slot,
-                                  int E, int C, int taps, cudaStream_t s);
+cudaError_t nrl_causal_conv(const float* in, long si, const float* in_bias, int act, const float* w, const float* bias,
+                            const float* state, float* out, long so, const int* cu, const int* tok_entry, const int* start,
+                            const int* state_slot, int T, int E, int C, int taps, cudaStream_t s);
+cudaError_t nrl_causal_conv_carry(const float* in, long si, const float* in_bias, float* state, const int* cu, const int* start,
+                                  const int* state_slot, int E, int C, int taps, cudaStream_t s);
 
 // State-space scan (scalar decay per head).  xbc float [T, *] (row stride sx): x at column 0 (heads*P), B at col_b, C at col_c
 // (groups*N each).  dt_raw float (row stride sd) [T, heads].  state float [slots, heads, N, P].
@@ -71,12 +105,21 @@ cudaError_t nrl_qknorm_kv_write(float* q, long sq, const float* k, long sk, cons
                                 float eps, void* k_cache, void* v_cache, int cache_f32, const int* kv_slot, int T, int Hq, int Hkv,
                                 int D, int Dv, int page, cudaStream_t s);
 
-// Sliding-window softmax attention over the paged cache: token at position p sees keys p-window+1 .. p.
-// out typed (row stride so) = out_scale * softmax(scale q.k) v.  single_token: every entry of the step holds one token.
+// Keys and values of a step's tokens into their pages, the values optionally blended with another layer's values of the
+// same tokens:  v <- (1 - lambda[0]) v + lambda[0] v_other  (v_other float, row stride svo, null: plain copy; lambda on device).
+// k float [T, Hkv*D] (row stride sk), v float [T, Hkv*Dv] (row stride sv); v is also updated in place when blended.
+cudaError_t nrl_kv_write_blend(const float* k, long sk, float* v, long sv, const float* v_other, long svo, const float* lambda,
+                               void* k_cache, void* v_cache, int cache_f32, const int* kv_slot, int T, int Hkv, int D, int Dv, int page,
+                               cudaStream_t s);
+
+// Softmax attention over the paged cache: token at position p sees keys p-window+1 .. p (or, mods->chunked, the keys of its
+// chunk up to p).  out typed (row stride so) = out_scale * softmax(scale q.k) v, with the optional terms of `mods` (null: none).
+// single_token: every entry of the step holds one token.
 cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, const void* v_cache, int cache_f32,
                                  const int* block_table, int max_blocks, const int* tok_entry, const int* pos, int window,
                                  float scale, float out_scale, void* out, long so, int out_f32, int T, int Hq, int Hkv, int D,
-                                 int Dv, int page, int single_token, int impl, int nsplit, float* part, cudaStream_t s);
+                                 int Dv, int page, int single_token, int impl, int nsplit, float* part, const NrlAttnMods* mods,
+                                 cudaStream_t s);
 // `nsplit` >= 1 with `part` float [T, Hq, 4 nsplit, Dv + 2] (steps of single tokens over bf16 pages): every warp of nsplit
 // blocks per (token, key/value head) walks its own pages and a second launch merges the parts; nrl_window_attention_splits
 // proposes the count (0: the shape does not fit).

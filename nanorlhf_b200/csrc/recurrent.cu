@@ -20,8 +20,8 @@ __device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : log1p
 // ---------------------------------------------------------------------------------------------------------------------
 // causal convolution: thread per (token, channel)
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void causal_conv_kernel(const float* __restrict__ in, long si, const float* __restrict__ w, const float* __restrict__ bias,
-                                   const float* __restrict__ state, float* __restrict__ out, long so, const int* __restrict__ cu,
+__global__ void causal_conv_kernel(const float* __restrict__ in, long si, const float* __restrict__ in_bias, int act,
+                                   const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state, float* __restrict__ out, long so, const int* __restrict__ cu,
                                    const int* __restrict__ tok_entry, const int* __restrict__ start,
                                    const int* __restrict__ state_slot, long T, int C, int taps) {
   const long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
@@ -34,14 +34,15 @@ __global__ void causal_conv_kernel(const float* __restrict__ in, long si, const 
   const bool carried = start[e] > 0;
   const float* st = state + static_cast<long>(state_slot[e]) * (taps - 1) * C;
   float acc = bias != nullptr ? bias[c] : 0.f;
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
   for (int j = 0; j < taps; ++j) {
     const int src = local - (taps - 1 - j);
     float x = 0.f;
-    if (src >= 0) x = in[(first + src) * si + c];
+    if (src >= 0) x = in[(first + src) * si + c] + ib;
     else if (carried) x = st[static_cast<long>(taps - 1 + src) * C + c];
     acc += w[static_cast<long>(c) * taps + j] * x;
   }
-  out[t * so + c] = silu(acc);
+  out[t * so + c] = act ? silu(acc) : acc;
 }
 
 // thread per (channel, run of kConvTok consecutive tokens): the last taps-1 inputs slide through registers, so every input is
@@ -49,8 +50,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ in, long si, const 
 constexpr int kConvTok = 8;
 
 template <int MAXT>
-__global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, const float* __restrict__ w, const float* __restrict__ bias,
-                                       const float* __restrict__ state, float* __restrict__ out, long so, const int* __restrict__ cu,
+__global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, const float* __restrict__ in_bias, int act,
+                                       const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state, float* __restrict__ out, long so, const int* __restrict__ cu,
                                        const int* __restrict__ tok_entry, const int* __restrict__ start,
                                        const int* __restrict__ state_slot, int T, int C, int taps) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -63,6 +64,7 @@ __global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, co
     hist[j] = 0.f;
   }
   const float b = bias != nullptr ? bias[c] : 0.f;
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
   int e_prev = -1;
   for (int t = t_begin; t < t_end; ++t) {
     const int e = tok_entry[t];
@@ -76,14 +78,14 @@ __global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, co
         if (j < taps - 1) {
           const int src = local - (taps - 1 - j);
           float x = 0.f;
-          if (src >= 0) x = in[(first + src) * si + c];
+          if (src >= 0) x = in[(first + src) * si + c] + ib;
           else if (carried) x = st[static_cast<long>(taps - 1 + src) * C + c];
           hist[j] = x;
         }
       }
       e_prev = e;
     }
-    const float cur = in[static_cast<long>(t) * si + c];
+    const float cur = in[static_cast<long>(t) * si + c] + ib;
     float acc = b;
 #pragma unroll
     for (int j = 0; j < MAXT - 1; ++j)
@@ -91,7 +93,7 @@ __global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, co
 #pragma unroll
     for (int j = 0; j < MAXT; ++j)
       if (j == taps - 1) acc += wv[j] * cur;
-    out[static_cast<long>(t) * so + c] = silu(acc);
+    out[static_cast<long>(t) * so + c] = act ? silu(acc) : acc;
 #pragma unroll
     for (int j = 0; j < MAXT - 1; ++j) {
       if (j < taps - 2) hist[j] = hist[j + 1];
@@ -101,7 +103,8 @@ __global__ void causal_conv_run_kernel(const float* __restrict__ in, long si, co
 }
 
 // thread per (entry, channel): the slot keeps the last taps-1 inputs of the sequence, oldest first
-__global__ void causal_conv_carry_kernel(const float* __restrict__ in, long si, float* __restrict__ state, const int* __restrict__ cu,
+__global__ void causal_conv_carry_kernel(const float* __restrict__ in, long si, const float* __restrict__ in_bias,
+                                         float* __restrict__ state, const int* __restrict__ cu,
                                          const int* __restrict__ start, const int* __restrict__ state_slot, int E, int C, int taps) {
   const long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
   if (idx >= static_cast<long>(E) * C) return;
@@ -112,12 +115,13 @@ __global__ void causal_conv_carry_kernel(const float* __restrict__ in, long si, 
   const bool carried = start[e] > 0;
   float* st = state + static_cast<long>(state_slot[e]) * (taps - 1) * C;
   float keep[kMaxTaps];
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
 #pragma unroll
   for (int j = 0; j < kMaxTaps; ++j) {
     if (j < taps - 1) {
       const int src = n - (taps - 1) + j;
       float x = 0.f;
-      if (src >= 0) x = in[(first + src) * si + c];
+      if (src >= 0) x = in[(first + src) * si + c] + ib;
       else if (carried) x = st[static_cast<long>(taps - 1 + src) * C + c];
       keep[j] = x;
     }
@@ -707,31 +711,31 @@ int pick_rows(int cols, int rows) {
 
 extern "C" {
 
-cudaError_t nrl_causal_conv(const float* in, long si, const float* w, const float* bias, const float* state, float* out, long so,
-                            const int* cu, const int* tok_entry, const int* start, const int* state_slot, int T, int E, int C,
-                            int taps, cudaStream_t s) {
+cudaError_t nrl_causal_conv(const float* in, long si, const float* in_bias, int act, const float* w, const float* bias,
+                            const float* state, float* out, long so, const int* cu, const int* tok_entry, const int* start,
+                            const int* state_slot, int T, int E, int C, int taps, cudaStream_t s) {
   if (T <= 0 || C <= 0) return cudaSuccess;
   if (taps < 1 || taps > kMaxTaps) return cudaErrorInvalidValue;
   if (T >= 2 * kConvTok && T >= 2 * E && (T + kConvTok - 1) / kConvTok <= 65535) {     // prompt portions: runs of tokens per thread
     const dim3 grid((C + 127) / 128, (T + kConvTok - 1) / kConvTok);
     if (taps <= 4)
-      causal_conv_run_kernel<4><<<grid, 128, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start, state_slot, T, C, taps);
+      causal_conv_run_kernel<4><<<grid, 128, 0, s>>>(in, si, in_bias, act, w, bias, state, out, so, cu, tok_entry, start, state_slot, T, C, taps);
     else
-      causal_conv_run_kernel<kMaxTaps><<<grid, 128, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start, state_slot, T, C, taps);
+      causal_conv_run_kernel<kMaxTaps><<<grid, 128, 0, s>>>(in, si, in_bias, act, w, bias, state, out, so, cu, tok_entry, start, state_slot, T, C, taps);
     return cudaGetLastError();
   }
   const long n = static_cast<long>(T) * C;
-  causal_conv_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(in, si, w, bias, state, out, so, cu, tok_entry, start,
-                                                                           state_slot, T, C, taps);
+  causal_conv_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(in, si, in_bias, act, w, bias, state, out, so, cu,
+                                                                           tok_entry, start, state_slot, T, C, taps);
   return cudaGetLastError();
 }
 
-cudaError_t nrl_causal_conv_carry(const float* in, long si, float* state, const int* cu, const int* start, const int* state_slot,
-                                  int E, int C, int taps, cudaStream_t s) {
+cudaError_t nrl_causal_conv_carry(const float* in, long si, const float* in_bias, float* state, const int* cu, const int* start,
+                                  const int* state_slot, int E, int C, int taps, cudaStream_t s) {
   if (E <= 0 || C <= 0 || taps <= 1) return cudaSuccess;
   if (taps > kMaxTaps) return cudaErrorInvalidValue;
   const long n = static_cast<long>(E) * C;
-  causal_conv_carry_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, s>>>(in, si, state, cu, start, state_slot, E, C, taps);
+  causal_conv_carry_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, s>>>(in, si, in_bias, state, cu, start, state_slot, E, C, taps);
   return cudaGetLastError();
 }
 

@@ -1,5 +1,6 @@
 // Residual-stream and normalisation kernels of hybrid decoders (float stream, typed GEMM operands):
-// learned-position embedding, depth-weighted stream + single-gain RMS norm, part-wise gated RMS norm, column activations.
+// learned-position and hashed-pair embeddings, depth-weighted stream + single-gain RMS norm, sandwich (pre + post) group norms
+// with a gated residual, part-wise gated RMS norm, column activations, mixture-of-experts routing.
 // Compiled WITHOUT fast-math: the float32 serving mode must stay within float rounding of a plain evaluation.
 #include <cuda_bf16.h>
 
@@ -112,6 +113,145 @@ __global__ void stream_norm_kernel(float* __restrict__ results, long stride_r, i
 #pragma unroll
     for (int k = 0; k < V; ++k) x[k] *= r;
     stv<V>(h + row + c, x);
+  }
+}
+
+// x[t] = embed[tok[t]] * scale + pair[row], row = (prev * mul_prev + tok * mul_cur) mod buckets, or row `buckets` for the first
+// token of a sequence.  prev comes from the step's own tokens or, for the first token of an entry, from the sequence's slot.
+template <typename WT>
+__global__ void embed_hashed_kernel(const WT* __restrict__ embed, const WT* __restrict__ pair, const int* __restrict__ tok,
+                                    const int* __restrict__ cu, const int* __restrict__ tok_entry, const int* __restrict__ start,
+                                    const int* __restrict__ state_slot, const int* __restrict__ prev_state, float scale,
+                                    long mul_prev, long mul_cur, long buckets, float* __restrict__ out, int W) {
+  const long t = blockIdx.x;
+  const int cur = tok[t];
+  const long a = static_cast<long>(cur) * W;
+  long b = -1;
+  if (pair != nullptr) {
+    const int e = tok_entry[t];
+    long row = buckets;
+    if (t > cu[e]) row = (static_cast<long>(tok[t - 1]) * mul_prev + static_cast<long>(cur) * mul_cur) % buckets;
+    else if (start[e] > 0) row = (static_cast<long>(prev_state[state_slot[e]]) * mul_prev + static_cast<long>(cur) * mul_cur) % buckets;
+    b = row * W;
+  }
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = ld(embed, a + c) * scale;
+    if (b >= 0) v += ld(pair, b + c);
+    out[t * W + c] = v;
+  }
+}
+
+__global__ void token_carry_kernel(const int* __restrict__ tok, const int* __restrict__ cu, const int* __restrict__ state_slot,
+                                   int* __restrict__ prev_state, int E) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < E) prev_state[state_slot[e]] = tok[cu[e + 1] - 1];
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+
+// Sublayer boundary of a sandwich-normed stream, one block per token; the vector is cut into `groups` equal parts and each
+// part has its own root mean square:
+//   if (o)  y = o * sigmoid(gate + gate_bias)  (gate == nullptr: y = o);  x += y / rms_part(y) * w_post
+//   if (h)  h = x / rms_part(x) * w_pre
+template <typename HT>
+__global__ void group_norm_residual_kernel(float* __restrict__ x, const float* __restrict__ o, const float* __restrict__ gate, long sg,
+                                           const float* __restrict__ gate_bias, const float* __restrict__ w_post,
+                                           const float* __restrict__ w_pre, int groups, float eps, HT* __restrict__ h, int W) {
+  __shared__ float red[32];
+  const long row = static_cast<long>(blockIdx.x) * W;
+  const int part = W / groups;
+  const float inv = 1.f / static_cast<float>(part);
+  for (int g = 0; g < groups; ++g) {
+    const int c0 = g * part, c1 = c0 + part;
+    if (o != nullptr) {
+      float ss = 0.f;
+      for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+        float y = o[row + c];
+        if (gate != nullptr) y *= sigmoidf_(gate[blockIdx.x * sg + c] + (gate_bias != nullptr ? gate_bias[c] : 0.f));
+        ss += y * y;
+      }
+      ss = block_sum(ss, red);
+      const float r = 1.f / sqrtf(ss * inv + eps);
+      for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+        float y = o[row + c];
+        if (gate != nullptr) y *= sigmoidf_(gate[blockIdx.x * sg + c] + (gate_bias != nullptr ? gate_bias[c] : 0.f));
+        x[row + c] += y * r * w_post[c];
+      }
+    }
+    if (h != nullptr) {
+      float ss = 0.f;
+      for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {       // a thread re-reads the columns it wrote itself
+        const float v = x[row + c];
+        ss += v * v;
+      }
+      ss = block_sum(ss, red);
+      const float r = 1.f / sqrtf(ss * inv + eps);
+      for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) st(h, row + c, x[row + c] * r * w_pre[c]);
+    }
+  }
+}
+
+// Mixture-of-experts routing and (dense form) expert activations, one block per token.
+//   z = router[t, :E] + router_bias;  the `top` largest (ties: lowest index) get softmax(z over the chosen) as weights
+//   ids [T, top] int, wts [T, top] float (if not null)
+//   act != nullptr:  act[t, e*ff + c] = weight_e * silu(gu[t, e*2ff + c]) * gu[t, e*2ff + ff + c], 0 for experts not chosen
+template <typename OT>
+__global__ void moe_route_kernel(const float* __restrict__ router, long sr, const float* __restrict__ router_bias, int E, int top,
+                                 const float* __restrict__ gu, long sgu, int ff, OT* __restrict__ act, long sa, int* __restrict__ ids,
+                                 float* __restrict__ wts) {
+  extern __shared__ float smf[];
+  float* z = smf;                 // [E]
+  float* wsel = z + E;            // [E]: weight, 0 = not chosen
+  const long t = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    z[e] = router[t * sr + e] + (router_bias != nullptr ? router_bias[e] : 0.f);
+    wsel[e] = 0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float zmax = 0.f, denom = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int bi = E;
+      for (int e = lane; e < E; e += 32) {
+        const float v = z[e];
+        if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (k == 0) zmax = best;
+      const float p = expf(best - zmax);
+      denom += p;
+      __syncwarp();
+      if (lane == 0) {
+        wsel[bi] = p;
+        z[bi] = -INFINITY;            // taken
+        if (ids != nullptr) ids[t * top + k] = bi;
+      }
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) wsel[e] = wsel[e] / denom;
+    __syncwarp();
+    if (wts != nullptr)
+      for (int k = lane; k < top; k += 32) wts[t * top + k] = wsel[ids[t * top + k]];
+  }
+  __syncthreads();
+  if (act == nullptr) return;
+  const long n = static_cast<long>(E) * ff;
+  for (long idx = threadIdx.x; idx < n; idx += blockDim.x) {
+    const int e = static_cast<int>(idx / ff), c = static_cast<int>(idx - static_cast<long>(e) * ff);
+    const float w = wsel[e];
+    float v = 0.f;
+    if (w != 0.f) {
+      const float gt = gu[t * sgu + static_cast<long>(e) * 2 * ff + c], up = gu[t * sgu + static_cast<long>(e) * 2 * ff + ff + c];
+      v = w * (gt * sigmoidf_(gt) * up);
+    }
+    st(act, t * sa + idx, v);
   }
 }
 
@@ -270,6 +410,52 @@ cudaError_t nrl_embed_pos(const void* embed, const void* pos_table, int w_f32, c
   else
     embed_pos_kernel<__nv_bfloat16><<<T, th, 0, s>>>(static_cast<const __nv_bfloat16*>(embed),
                                                     static_cast<const __nv_bfloat16*>(pos_table), tok, pos, out, W);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_embed_hashed(const void* embed, const void* pair, int w_f32, const int* tok, const int* cu, const int* tok_entry,
+                             const int* start, const int* state_slot, int* prev_state, float scale, long mul_prev, long mul_cur,
+                             long buckets, float* out, int T, int E, int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  const int th = W >= 256 ? 256 : 128;
+  if (w_f32)
+    embed_hashed_kernel<float><<<T, th, 0, s>>>(static_cast<const float*>(embed), static_cast<const float*>(pair), tok, cu, tok_entry,
+                                                start, state_slot, prev_state, scale, mul_prev, mul_cur, buckets, out, W);
+  else
+    embed_hashed_kernel<__nv_bfloat16><<<T, th, 0, s>>>(static_cast<const __nv_bfloat16*>(embed),
+                                                        static_cast<const __nv_bfloat16*>(pair), tok, cu, tok_entry, start, state_slot,
+                                                        prev_state, scale, mul_prev, mul_cur, buckets, out, W);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || prev_state == nullptr) return e;
+  token_carry_kernel<<<(E + 127) / 128, 128, 0, s>>>(tok, cu, state_slot, prev_state, E);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_group_norm_residual(float* x, const float* o, const float* gate, long sg, const float* gate_bias, const float* w_post,
+                                    const float* w_pre, int groups, float eps, void* h, int h_f32, int T, int W, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (groups < 1 || W % groups != 0 || (o != nullptr && w_post == nullptr) || (h != nullptr && w_pre == nullptr)) return cudaErrorInvalidValue;
+  const int part = W / groups;
+  const int th = part >= 1024 ? 256 : part >= 128 ? 128 : 64;
+  if (h_f32)
+    group_norm_residual_kernel<float><<<T, th, 0, s>>>(x, o, gate, sg, gate_bias, w_post, w_pre, groups, eps, static_cast<float*>(h), W);
+  else
+    group_norm_residual_kernel<__nv_bfloat16><<<T, th, 0, s>>>(x, o, gate, sg, gate_bias, w_post, w_pre, groups, eps,
+                                                               static_cast<__nv_bfloat16*>(h), W);
+  return cudaGetLastError();
+}
+
+cudaError_t nrl_moe_route(const float* router, long sr, const float* router_bias, int E, int top, const float* gu, long sgu, int ff,
+                          void* act, long sa, int act_f32, int* ids, float* wts, int T, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  if (E < 1 || top < 1 || top > E || E > 4096 || (wts != nullptr && ids == nullptr)) return cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * 2 * E;
+  const int th = act == nullptr ? 32 : 256;
+  if (act_f32)
+    moe_route_kernel<float><<<T, th, smem, s>>>(router, sr, router_bias, E, top, gu, sgu, ff, static_cast<float*>(act), sa, ids, wts);
+  else
+    moe_route_kernel<__nv_bfloat16><<<T, th, smem, s>>>(router, sr, router_bias, E, top, gu, sgu, ff, static_cast<__nv_bfloat16*>(act),
+                                                        sa, ids, wts);
   return cudaGetLastError();
 }
 

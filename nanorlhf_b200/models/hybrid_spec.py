@@ -1,0 +1,158 @@
+"""What the step engine (sampler/hybrid_sampler.py) needs to know about a hybrid decoder: generic descriptions of its token
+mixers, feed-forwards and residual stream, and a module that holds checkpoint tensors under their own names.
+
+A model family (models/nezavik.py, models/vilosun.py) turns its ``config.json`` into these specs; the engine executes them
+with the kernels of ``ops/hybrid.py``.  Model files contain no forward loop.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from .hf_io import load_state_dict, save_state_dict
+
+
+@dataclass
+class MixerSpec:
+    """One token mixer of a layer.  ``kind``: window_attention | conv_attention | ssd | gated_delta.  ``prefix``: tensor-name prefix."""
+    kind: str
+    prefix: str
+    out_scale: float = 1.0
+    heads: int = 0
+    kv_heads: int = 0            # key/value heads (attention), q/k heads (delta rule), groups (ssd)
+    dim: int = 0                 # query/key size per head; state size N (ssd)
+    vdim: int = 0                # value size per head
+    window: int = 0              # attention: keys seen, the token itself included (mask "window"); chunk length (mask "chunk")
+    scale: float = 1.0           # attention: score multiplier
+    conv: int = 0                # taps of the short causal convolution
+    norm_groups: int = 1         # ssd: equal parts of the gated RMS norm
+    per_channel: bool = False    # delta rule: decay per head and key channel + low-rank sigmoid gate
+    # conv_attention (biased projections, short convolution on q / k / v, no q / k norm, no rotation):
+    mask: str = "window"         # "window": the last `window` keys; "chunk": the keys of the query's own chunk of `window` positions
+    slope_exp: float = 0.0       # > 0: head h's score loses 2^(-slope_exp (h + 1) / heads) per position of distance
+    head_temp: bool = False      # learned score multiplier per head (tensor "temp")
+    head_gate: bool = False      # head output times sigmoid of a per-head projection of the mixer's input (tensor "g")
+    v_blend: int = -1            # -1: none; else the layer whose values this layer's values are blended with (tensor "vmix"),
+                                 # its own index for the layer that only provides them
+
+
+@dataclass
+class LayerSpec:
+    index: int
+    mixers: List[MixerSpec]
+    ff: int = 0                  # 0: no feed-forward; else its inner width (of one expert for "moe")
+    ff_act: str = "relu2"        # "relu2": W_down relu(W_up h)^2;  "swiglu": W_down (silu(W_gate h) * W_up h)
+    ff_kind: str = "dense"       # "dense" | "moe" (experts e0.., top-k router with softmax over the chosen logits)
+    experts: int = 0
+    top: int = 0
+
+
+@dataclass
+class StreamSpec:
+    """How layers read and write the residual stream, and what surrounds them.
+
+    ``kind`` "depth_weighted": every layer reads one single-gain RMS norm of a learned weighted sum of all earlier results and
+    adds ``mixer + ff`` of it (tensors norm1, dwa).  ``kind`` "sandwich": ``x += norm1b(g1 * mixer(norm1 x))`` then
+    ``x += norm2b(g2 * ff(norm2 x))`` with group RMS norms (a weight per column) and, when ``gated_residual``, sigmoid gates
+    ``g = sigmoid(rg h + rg.b)`` of the sublayer's input."""
+    kind: str = "depth_weighted"
+    norm_groups: int = 1
+    gated_residual: bool = False
+    embed_scale: float = 1.0
+    positions: bool = True                      # learned position vectors added to the embedding (tensor "pos")
+    pair_buckets: int = 0                       # > 0: hashed (previous token, token) embedding rows (tensor "bigram")
+    pair_mul_prev: int = 0
+    pair_mul_cur: int = 0
+    logit_scale: float = 1.0
+
+
+def _mangle(name: str) -> str:
+    return name.replace(".", "__")
+
+
+class TensorModel(nn.Module):
+    """Holds the checkpoint tensors (``tensor(name)``) of a hybrid decoder; executed by ``sampler.hybrid_sampler.HybridSampler``.
+
+    Subclasses set ``config_class`` (with ``from_pretrained`` / ``to_dict`` / ``layer_specs`` / ``stream_spec`` /
+    ``tensor_shapes``) and may override ``free_shape`` (tensors whose shape the config does not fix) and ``init_value``."""
+    config_class = None
+    int_tensors = ()                            # names stored as int32
+
+    def __init__(self, cfg, shapes: Optional[Dict[str, tuple]] = None, dtype=torch.bfloat16, device="cpu"):
+        super().__init__()
+        self.config = cfg
+        shapes = shapes or cfg.tensor_shapes()
+        self.names = list(shapes)
+        self.weights = nn.ParameterDict({_mangle(n): nn.Parameter(torch.empty(shapes[n], dtype=dtype, device=device),
+                                                                  requires_grad=False) for n in self.names})
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self.weights[_mangle(name)]
+
+    def has_tensor(self, name: str) -> bool:
+        return _mangle(name) in self.weights
+
+    def layer_specs(self) -> List[LayerSpec]:
+        return self.config.layer_specs()
+
+    def stream_spec(self) -> StreamSpec:
+        return self.config.stream_spec()
+
+    @property
+    def device(self):
+        return next(self.parameters()).device
+
+    @property
+    def dtype(self):
+        return next(self.parameters()).dtype
+
+    @staticmethod
+    def free_shape(name: str) -> bool:
+        return False
+
+    # ---- checkpoint I/O (config.json + model.safetensors, tensors under their own names) ----
+    @classmethod
+    def from_pretrained(cls, path: str, torch_dtype=torch.bfloat16, device="cpu", **_):
+        cfg = cls.config_class.from_pretrained(path)
+        sd = load_state_dict(os.path.join(path, "model.safetensors"))
+        want = cfg.tensor_shapes()
+        missing = [n for n in want if n not in sd]
+        extra = [n for n in sd if n not in want]
+        if missing or extra:
+            raise ValueError(f"checkpoint does not fit its config: missing {missing[:4]}, unexpected {extra[:4]}")
+        shapes = {n: tuple(sd[n].shape) for n in want}
+        for n, shp in want.items():
+            if shapes[n] != tuple(shp) and not cls.free_shape(n):
+                raise ValueError(f"tensor {n}: shape {shapes[n]} does not fit the config ({tuple(shp)})")
+        model = cls(cfg, shapes, dtype=torch_dtype, device=device)
+        with torch.no_grad():
+            for n in model.names:
+                model.tensor(n).copy_(sd[n].to(torch_dtype))
+        return model
+
+    def save_pretrained(self, path: str):
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.config.to_dict(), f, indent=1)
+        save_state_dict({n: self.tensor(n) for n in self.names}, os.path.join(path, "model.safetensors"))
+
+    @staticmethod
+    def init_value(name: str, t: torch.Tensor, g: torch.Generator) -> torch.Tensor:
+        raise NotImplementedError
+
+    @classmethod
+    def from_config(cls, cfg, torch_dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None, **shape_kw):
+        """Random weights (benchmarks, smoke tests)."""
+        model = cls(cfg, cfg.tensor_shapes(**shape_kw), dtype=torch_dtype, device=device)
+        g = torch.Generator(device="cpu")
+        g.manual_seed(0 if seed is None else seed)
+        with torch.no_grad():
+            for n in model.names:
+                t = model.tensor(n)
+                t.copy_(cls.init_value(n, t, g).to(torch_dtype))
+        return model

@@ -25,35 +25,9 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 import torch
-import torch.nn as nn
 
-from .hf_io import load_state_dict, save_state_dict
+from .hybrid_spec import LayerSpec, MixerSpec, StreamSpec, TensorModel
 from .registry import register_model
-
-
-@dataclass
-class MixerSpec:
-    """One token mixer of a layer.  ``kind``: window_attention | ssd | gated_delta.  ``prefix``: tensor-name prefix."""
-    kind: str
-    prefix: str
-    out_scale: float = 1.0
-    heads: int = 0
-    kv_heads: int = 0            # key/value heads (attention), q/k heads (delta rule), groups (ssd)
-    dim: int = 0                 # query/key size per head; state size N (ssd)
-    vdim: int = 0                # value size per head
-    window: int = 0              # attention: keys seen, the token itself included
-    scale: float = 1.0           # attention: score multiplier
-    conv: int = 0                # taps of the short causal convolution
-    norm_groups: int = 1         # ssd: equal parts of the gated RMS norm
-    per_channel: bool = False    # delta rule: decay per head and key channel + low-rank sigmoid gate
-
-
-@dataclass
-class LayerSpec:
-    index: int
-    mixers: List[MixerSpec]
-    ff: int = 0                  # 0: no feed-forward
-    ff_act: str = "relu2"
 
 
 @dataclass
@@ -125,6 +99,9 @@ class NezavikConfig:
             specs.append(LayerSpec(i, mixers, ff=int(mlp["ff"]) if mlp is not None else 0))
         return specs
 
+    def stream_spec(self) -> StreamSpec:
+        return StreamSpec(kind="depth_weighted", positions=True)
+
     def tensor_shapes(self, rank: int = 16) -> Dict[str, tuple]:
         """Name -> shape of every checkpoint tensor (``rank``: width of the low-rank decay / gate projections, which a
         checkpoint fixes by the shape of ``a1``)."""
@@ -160,92 +137,38 @@ class NezavikConfig:
         return out
 
 
-def _mangle(name: str) -> str:
-    return name.replace(".", "__")
-
-
 @register_model("Nezavik", sampler="hybrid")
-class NezavikForCausalLM(nn.Module):
-    """Holds the checkpoint tensors (``tensor(name)``); executed by ``sampler.hybrid_sampler.HybridSampler``."""
+class NezavikForCausalLM(TensorModel):
+    """Nezavik checkpoint tensors under their own names; executed by ``sampler.hybrid_sampler.HybridSampler``."""
+    config_class = NezavikConfig
 
-    def __init__(self, cfg: NezavikConfig, shapes: Optional[Dict[str, tuple]] = None, dtype=torch.bfloat16, device="cpu"):
-        super().__init__()
-        self.config = cfg
-        shapes = shapes or cfg.tensor_shapes()
-        self.names = list(shapes)
-        self.weights = nn.ParameterDict({_mangle(n): nn.Parameter(torch.empty(shapes[n], dtype=dtype, device=device),
-                                                                  requires_grad=False) for n in self.names})
-
-    def tensor(self, name: str) -> torch.Tensor:
-        return self.weights[_mangle(name)]
-
-    def has_tensor(self, name: str) -> bool:
-        return _mangle(name) in self.weights
-
-    def layer_specs(self) -> List[LayerSpec]:
-        return self.config.layer_specs()
-
-    @property
-    def device(self):
-        return next(self.parameters()).device
-
-    @property
-    def dtype(self):
-        return next(self.parameters()).dtype
-
-    # ---- checkpoint I/O (config.json + model.safetensors, tensors under their own names) ----
-    @classmethod
-    def from_pretrained(cls, path: str, torch_dtype=torch.bfloat16, device="cpu", **_):
-        cfg = NezavikConfig.from_pretrained(path)
-        sd = load_state_dict(os.path.join(path, "model.safetensors"))
-        want = cfg.tensor_shapes()
-        missing = [n for n in want if n not in sd]
-        extra = [n for n in sd if n not in want]
-        if missing or extra:
-            raise ValueError(f"checkpoint does not fit its config: missing {missing[:4]}, unexpected {extra[:4]}")
-        shapes = {n: tuple(sd[n].shape) for n in want}
-        for n, shp in want.items():                      # only the low-rank width is free
-            free = n.endswith((".a1", ".g1", ".a2", ".g2"))
-            if shapes[n] != tuple(shp) and not free:
-                raise ValueError(f"tensor {n}: shape {shapes[n]} does not fit the config ({tuple(shp)})")
-        model = cls(cfg, shapes, dtype=torch_dtype, device=device)
-        with torch.no_grad():
-            for n in model.names:
-                model.tensor(n).copy_(sd[n].to(torch_dtype))
-        return model
-
-    def save_pretrained(self, path: str):
-        os.makedirs(path, exist_ok=True)
-        with open(os.path.join(path, "config.json"), "w") as f:
-            json.dump(self.config.to_dict(), f, indent=1)
-        save_state_dict({n: self.tensor(n) for n in self.names}, os.path.join(path, "model.safetensors"))
+    @staticmethod
+    def free_shape(name: str) -> bool:                   # only the low-rank width is free
+        return name.endswith((".a1", ".g1", ".a2", ".g2"))
 
     @classmethod
     def from_config(cls, cfg: NezavikConfig, torch_dtype=torch.bfloat16, device="cpu", seed: Optional[int] = None, rank: int = 16):
         """Random weights (benchmarks, smoke tests): projections ~ N(0, 1/fan_in), decays and gains in a stable range."""
-        model = cls(cfg, cfg.tensor_shapes(rank), dtype=torch_dtype, device=device)
-        g = torch.Generator(device="cpu")
-        g.manual_seed(0 if seed is None else seed)
-        with torch.no_grad():
-            for n in model.names:
-                t = model.tensor(n)
-                leaf = n.rsplit(".", 1)[-1]
-                if t.dim() == 2 and leaf != "conv":
-                    v = torch.randn(t.shape, generator=g) / (t.shape[1] ** 0.5)
-                    if leaf in ("embed", "pos"):
-                        v = torch.randn(t.shape, generator=g) * (1.0 if leaf == "embed" else 0.3)
-                elif leaf == "conv":
-                    v = torch.randn(t.shape, generator=g) / (t.shape[1] ** 0.5)
-                elif leaf == "dwa":
-                    v = torch.rand(t.shape, generator=g) + 0.2
-                    v = v / v.sum()
-                elif leaf == "A_log":
-                    v = torch.rand(t.shape, generator=g) * 2.0 - 1.5
-                elif leaf == "dt_bias":
-                    v = torch.rand(t.shape, generator=g) * 2.5 - 3.0
-                elif leaf == "b" and t.dim() == 1:
-                    v = torch.rand(t.shape, generator=g) * 0.2 - 0.1
-                else:                                     # gains: norm1, q.norm, k.norm, norm, D, final.norm
-                    v = torch.rand(t.shape, generator=g) * 0.5 + 0.75
-                t.copy_(v.to(torch_dtype))
-        return model
+        return super().from_config(cfg, torch_dtype=torch_dtype, device=device, seed=seed, rank=rank)
+
+    @staticmethod
+    def init_value(n: str, t: torch.Tensor, g: torch.Generator) -> torch.Tensor:
+        leaf = n.rsplit(".", 1)[-1]
+        if t.dim() == 2 and leaf != "conv":
+            v = torch.randn(t.shape, generator=g) / (t.shape[1] ** 0.5)
+            if leaf in ("embed", "pos"):
+                v = torch.randn(t.shape, generator=g) * (1.0 if leaf == "embed" else 0.3)
+        elif leaf == "conv":
+            v = torch.randn(t.shape, generator=g) / (t.shape[1] ** 0.5)
+        elif leaf == "dwa":
+            v = torch.rand(t.shape, generator=g) + 0.2
+            v = v / v.sum()
+        elif leaf == "A_log":
+            v = torch.rand(t.shape, generator=g) * 2.0 - 1.5
+        elif leaf == "dt_bias":
+            v = torch.rand(t.shape, generator=g) * 2.5 - 3.0
+        elif leaf == "b" and t.dim() == 1:
+            v = torch.rand(t.shape, generator=g) * 0.2 - 0.1
+        else:                                     # gains: norm1, q.norm, k.norm, norm, D, final.norm
+            v = torch.rand(t.shape, generator=g) * 0.5 + 0.75
+        return v

@@ -11,7 +11,8 @@ import os
 from typing import Callable, Dict, Tuple
 
 _REGISTRY: Dict[str, Tuple[type, str]] = {}
-_LAZY = {"Qwen2ForCausalLM": "qwen2", "qwen2": "qwen2", "Nezavik": "nezavik", "nezavik": "nezavik"}
+_LAZY = {"Qwen2ForCausalLM": "qwen2", "qwen2": "qwen2", "Nezavik": "nezavik", "nezavik": "nezavik",
+         "Vilosun": "vilosun", "vilosun": "vilosun"}
 
 
 def register_model(*names: str, sampler: str = "native") -> Callable[[type], type]:

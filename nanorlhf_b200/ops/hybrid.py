@@ -36,9 +36,12 @@ def gated_part_rmsnorm(y, gate, w, part, gate_act, gate_first, eps, scale, out):
     _ext().gated_part_rmsnorm(y, gate, w, part, {"silu": 0, "sigmoid": 1}[gate_act], gate_first, eps, scale, out)
 
 
-def causal_conv(x, w, bias, state, out, plan):
+def causal_conv(x, w, bias, state, out, plan, in_bias=None, act: str = "silu"):
+    """``in_bias``: bias of the projection that made ``x`` (part of the convolved signal and of the carried taps); ``bias``: added
+    after the convolution; ``act``: "silu" or "none"."""
     native._count(2)
-    _ext().causal_conv(x, w, bias, state, out, plan.cu, plan.tok_entry, plan.start, plan.state_slot)
+    _ext().causal_conv(x, w, bias, state, out, plan.cu, plan.tok_entry, plan.start, plan.state_slot, in_bias,
+                       {"none": 0, "silu": 1}[act])
 
 
 SCAN_IMPLS = {"auto": 0, "column": 1, "rows": 2, "shared": 3}
@@ -69,9 +72,38 @@ def qknorm_kv_write(q, k, v, qw, kw, eps, k_cache, v_cache, plan):
 WINDOW_IMPLS = {"auto": 0, "tile": 1, "simple": 2, "mma": 3}
 
 
-def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out, impl: str = "auto"):
+def window_attention(q, k_cache, v_cache, plan, window, scale, out_scale, out, impl: str = "auto", chunked: bool = False,
+                     head_scale=None, head_slope=None, gate=None):
     """``impl``: "auto" (tensor cores for prompt portions over bf16 pages, the scalar tile kernel otherwise) or one kernel by
-    name; a kernel that does not fit the shapes raises."""
+    name; a kernel that does not fit the shapes raises.  ``chunked``: keys of the query's own chunk of ``window`` positions
+    instead of the last ``window`` keys.  ``head_scale`` / ``head_slope`` [heads]: per-head score multiplier and linear distance
+    penalty; ``gate`` [T, heads]: the head's output is multiplied by sigmoid(gate)."""
     native._count()
     _ext().window_attention(q, k_cache, v_cache, plan.block_table, plan.tok_entry, plan.pos, window, scale, out_scale, out,
-                            WINDOW_IMPLS[impl])
+                            WINDOW_IMPLS[impl], chunked, head_scale, head_slope, gate)
+
+
+def kv_write_blend(k, v, v_other, lam, k_cache, v_cache, plan):
+    """Keys and values into their pages; ``v <- (1 - lam) v + lam v_other`` first (in place) when ``v_other`` is given."""
+    native._count()
+    _ext().kv_write_blend(k, v, v_other, lam, k_cache, v_cache, plan.kv_slot)
+
+
+def embed_hashed(embed, pair, plan, prev_state, scale, mul_prev, mul_cur, buckets, out):
+    """x0 = embed[tok] * scale + pair[(prev * mul_prev + tok * mul_cur) % buckets] (row ``buckets`` at a sequence's start)."""
+    native._count(2 if pair is not None else 1)
+    _ext().embed_hashed(embed, pair, plan.tokens, plan.cu, plan.tok_entry, plan.start, plan.state_slot, prev_state, scale, mul_prev,
+                        mul_cur, buckets, out)
+    return out
+
+
+def group_norm_residual(x, o, gate, gate_bias, w_post, w_pre, groups, eps, h):
+    """``x += groupnorm(o * sigmoid(gate + gate_bias)) * w_post`` (when ``o`` is given), then ``h = groupnorm(x) * w_pre``."""
+    native._count()
+    _ext().group_norm_residual(x, o, gate, gate_bias, w_post, w_pre, groups, eps, h)
+
+
+def moe_route(router, router_bias, top, gu=None, ff=0, act=None, ids=None, wts=None):
+    """Top-k routing (softmax over the chosen logits); with ``gu`` / ``act`` also the dense-form expert activations."""
+    native._count()
+    _ext().moe_route(router, router_bias, top, gu, ff, act, ids, wts)

@@ -25,6 +25,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..models.hybrid_spec import StreamSpec
 from ..ops import gemm as _gemm, hybrid as hy, native
 
 
@@ -56,7 +57,10 @@ class _Mixer:
 
 
 class _Layer:
-    __slots__ = ("spec", "gain", "dw", "w_in", "w_out", "mixers", "ff_col", "ff_out_col", "n_in", "k_out", "out_pad")
+    """One pair of fused matrices with what runs between them: a whole layer of a depth-weighted stream (mixers and the
+    feed-forward side by side), or one sublayer of a sandwich stream (the mixer, or the feed-forward)."""
+    __slots__ = ("spec", "gain", "dw", "w_in", "w_out", "mixers", "ff_col", "ff_out_col", "n_in", "k_out", "out_pad",
+                 "w_pre", "w_post", "gate_col", "gate_bias", "router_col", "router_bias")
 
 
 def _pad8(n: int) -> int:
@@ -116,87 +120,142 @@ class HybridSampler:
     def _build_arena(self):
         lm, dev, wd = self.lm, self.device, self.wdtype
         W = self.cfg.width
+        self.stream = lm.stream_spec() if hasattr(lm, "stream_spec") else StreamSpec()
+        st = self.stream
         self.layers = []
         for spec in lm.layer_specs():
             p = f"l{spec.index}."
-            L = _Layer()
-            L.spec = spec
-            L.gain = self._f(p + "norm1").reshape(1)
-            L.dw = self._f(p + "dwa")
-            rows_in: List[torch.Tensor] = []
-            cols_out: List[torch.Tensor] = []
-            n_in = k_out = 0
-            L.mixers = []
-
-            def add_in(name):
-                nonlocal n_in
-                t = self._t(name)
-                rows_in.append(t)
-                c = (n_in, t.shape[0])
-                n_in += t.shape[0]
-                return c
-
-            def add_out(name):
-                nonlocal k_out
-                t = self._t(name)
-                cols_out.append(t)
-                c = k_out
-                k_out += t.shape[1]
-                return c, t.shape[1]
-
-            for ms in spec.mixers:
-                M = _Mixer()
-                M.spec, M.cols, M.vec = ms, {}, {}
-                M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = None
-                q = ms.prefix
-                if ms.kind == "window_attention":
-                    for n in ("q", "k", "v"):
-                        M.cols[n] = add_in(q + n)
-                    M.vec["qw"], M.vec["kw"] = self._f(q + "q.norm"), self._f(q + "k.norm")
-                elif ms.kind == "ssd":
-                    M.cols["in"] = add_in(q + "in")
-                    for n in ("conv", "conv.b", "dt_bias", "A_log", "D", "norm"):
-                        M.vec[n] = self._f(q + n)
-                elif ms.kind == "gated_delta":
-                    for n in ("q", "k", "v", "b"):
-                        M.cols[n] = add_in(q + n)
-                    if ms.per_channel:
-                        M.cols["a1"], M.cols["g1"] = add_in(q + "a1"), add_in(q + "g1")
-                        a2, g2 = self._t(q + "a2"), self._t(q + "g2")
-                        r = a2.shape[1]
-                        M.rank = r
-                        na, ng = a2.shape[0], g2.shape[0]
-                        w2 = torch.zeros(_pad8(na + ng), _pad8(2 * r), dtype=wd, device=dev)     # block diagonal: [a2 0; 0 g2]
-                        w2[:na, :r] = a2.to(wd)
-                        w2[na:na + ng, r:2 * r] = g2.to(wd)
-                        M.w_lr2, M.lr_cols = w2, (na, ng)
-                    else:
-                        M.cols["a"], M.cols["g"] = add_in(q + "a"), add_in(q + "g")
-                    M.vec["conv"] = torch.cat([self._f(q + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
-                    for n in ("dt_bias", "A_log", "norm"):
-                        M.vec[n] = self._f(q + n)
-                else:
-                    raise ValueError(f"unknown mixer kind {ms.kind!r}")
-                M.out_col, M.out_size = add_out(q + "o")
-                L.mixers.append(M)
-            L.ff_col = L.ff_out_col = None
-            if spec.ff:
-                L.ff_col = add_in(p + "mlp.up")
-                L.ff_out_col = add_out(p + "mlp.down")
-            L.n_in, L.k_out = _pad8(n_in), _pad8(k_out)
-            L.out_pad = L.k_out != k_out
-            L.w_in = torch.zeros(L.n_in, W, dtype=wd, device=dev)
-            L.w_in[:n_in] = torch.cat([t.to(device=dev, dtype=wd) for t in rows_in], 0)
-            L.w_out = torch.zeros(W, L.k_out, dtype=wd, device=dev)
-            L.w_out[:, :k_out] = torch.cat([t.to(device=dev, dtype=wd) for t in cols_out], 1)
-            self.layers.append(L)
+            if st.kind == "depth_weighted":               # one stage: mixers and feed-forward read the same norm
+                L = self._build_stage(spec, spec.mixers, True)
+                L.gain = self._f(p + "norm1").reshape(1)
+                L.dw = self._f(p + "dwa")
+                self.layers.append(L)
+            elif st.kind == "sandwich":                   # two stages: the mixer, then the feed-forward, each between its norms
+                for k, (mixers, ff) in enumerate(((spec.mixers, False), ([], True))):
+                    if ff and not spec.ff:
+                        continue
+                    n = str(k + 1)
+                    L = self._build_stage(spec, mixers, ff, gate=p + "rg" + n if st.gated_residual else None)
+                    L.w_pre, L.w_post = self._f(p + "norm" + n), self._f(p + "norm" + n + "b")
+                    self.layers.append(L)
+            else:
+                raise ValueError(f"unknown stream kind {st.kind!r}")
         self.embed = self._t("embed").to(device=dev, dtype=wd).contiguous()
-        self.pos_table = self._t("pos").to(device=dev, dtype=wd).contiguous()
-        self.final_gain = self._f("final.norm").reshape(1)
+        self.pos_table = self._t("pos").to(device=dev, dtype=wd).contiguous() if st.positions else None
+        self.pair_table = self._t("bigram").to(device=dev, dtype=wd).contiguous() if st.pair_buckets else None
+        self.final_gain = self._f("final.norm").reshape(1) if st.kind == "depth_weighted" else self._f("final.norm")
         V = self.cfg.vocab
         self.head = torch.zeros(_pad8(V), W, dtype=wd, device=dev)
         self.head[:V] = self._t("head").to(device=dev, dtype=wd)
         self._weights_version = self.weights_fingerprint()
+
+    def _build_stage(self, spec, mixer_specs, with_ff: bool, gate: Optional[str] = None) -> _Layer:
+        """Fuse every projection that reads the stage's normed input into ``w_in`` and every projection that writes the stream
+        into ``w_out``; keep the small vectors as float32."""
+        dev, wd, W = self.device, self.wdtype, self.cfg.width
+        p = f"l{spec.index}."
+        L = _Layer()
+        L.spec = spec
+        L.gain = L.dw = L.w_pre = L.w_post = L.gate_col = L.gate_bias = L.router_col = L.router_bias = None
+        rows_in: List[torch.Tensor] = []
+        cols_out: List[torch.Tensor] = []
+        n_in = k_out = 0
+        L.mixers = []
+
+        def add_in(name):
+            nonlocal n_in
+            t = self._t(name)
+            rows_in.append(t)
+            c = (n_in, t.shape[0])
+            n_in += t.shape[0]
+            return c
+
+        def add_out(name):
+            nonlocal k_out
+            t = self._t(name)
+            cols_out.append(t)
+            c = k_out
+            k_out += t.shape[1]
+            return c, t.shape[1]
+
+        for ms in mixer_specs:
+            M = _Mixer()
+            M.spec, M.cols, M.vec = ms, {}, {}
+            M.k_cache = M.v_cache = M.conv_state = M.state = M.w_lr2 = None
+            q = ms.prefix
+            if ms.kind == "window_attention":
+                for n in ("q", "k", "v"):
+                    M.cols[n] = add_in(q + n)
+                M.vec["qw"], M.vec["kw"] = self._f(q + "q.norm"), self._f(q + "k.norm")
+            elif ms.kind == "conv_attention":
+                for n in ("q", "k", "v"):
+                    M.cols[n] = add_in(q + n)
+                if ms.head_gate:
+                    M.cols["g"] = add_in(q + "g")
+                M.vec["conv"] = torch.cat([self._f(q + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
+                M.vec["in_bias"] = torch.cat([self._f(q + n + ".b") for n in ("q", "k", "v")], 0).contiguous()
+                if ms.head_temp:
+                    M.vec["temp"] = self._f(q + "temp")
+                if ms.slope_exp > 0:
+                    hs = torch.arange(1, ms.heads + 1, dtype=torch.float64)
+                    M.vec["slope"] = torch.exp2(-ms.slope_exp * hs / ms.heads).to(device=dev, dtype=torch.float32)
+                if ms.v_blend >= 0 and ms.v_blend != spec.index:
+                    M.vec["vmix"] = self._f(q + "vmix").reshape(1)
+            elif ms.kind == "ssd":
+                M.cols["in"] = add_in(q + "in")
+                for n in ("conv", "conv.b", "dt_bias", "A_log", "D", "norm"):
+                    M.vec[n] = self._f(q + n)
+            elif ms.kind == "gated_delta":
+                for n in ("q", "k", "v", "b"):
+                    M.cols[n] = add_in(q + n)
+                if ms.per_channel:
+                    M.cols["a1"], M.cols["g1"] = add_in(q + "a1"), add_in(q + "g1")
+                    a2, g2 = self._t(q + "a2"), self._t(q + "g2")
+                    r = a2.shape[1]
+                    M.rank = r
+                    na, ng = a2.shape[0], g2.shape[0]
+                    w2 = torch.zeros(_pad8(na + ng), _pad8(2 * r), dtype=wd, device=dev)     # block diagonal: [a2 0; 0 g2]
+                    w2[:na, :r] = a2.to(wd)
+                    w2[na:na + ng, r:2 * r] = g2.to(wd)
+                    M.w_lr2, M.lr_cols = w2, (na, ng)
+                else:
+                    M.cols["a"], M.cols["g"] = add_in(q + "a"), add_in(q + "g")
+                M.vec["conv"] = torch.cat([self._f(q + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
+                for n in ("dt_bias", "A_log", "norm"):
+                    M.vec[n] = self._f(q + n)
+            else:
+                raise ValueError(f"unknown mixer kind {ms.kind!r}")
+            M.out_col, M.out_size = add_out(q + "o")
+            L.mixers.append(M)
+        L.ff_col = L.ff_out_col = None
+        if with_ff and spec.ff:
+            if spec.ff_kind == "dense":
+                L.ff_col = add_in(p + "mlp.up")
+                L.ff_out_col = add_out(p + "mlp.down")
+            elif spec.ff_kind == "moe":                   # router, then per expert its gate rows and its up rows
+                L.router_col = add_in(p + "mlp.router")
+                L.router_bias = self._f(p + "mlp.router.b") if self.lm.has_tensor(p + "mlp.router.b") else None
+                c0 = n_in
+                for e in range(spec.experts):
+                    add_in(f"{p}mlp.e{e}.gate")
+                    add_in(f"{p}mlp.e{e}.up")
+                L.ff_col = (c0, n_in - c0)
+                c0 = k_out
+                for e in range(spec.experts):
+                    add_out(f"{p}mlp.e{e}.down")
+                L.ff_out_col = (c0, k_out - c0)
+            else:
+                raise ValueError(f"unknown feed-forward kind {spec.ff_kind!r}")
+        if gate is not None:
+            L.gate_col = add_in(gate)
+            L.gate_bias = self._f(gate + ".b") if self.lm.has_tensor(gate + ".b") else None
+        L.n_in, L.k_out = _pad8(n_in), _pad8(k_out)
+        L.out_pad = L.k_out != k_out
+        L.w_in = torch.zeros(L.n_in, W, dtype=wd, device=dev)
+        L.w_in[:n_in] = torch.cat([t.to(device=dev, dtype=wd) for t in rows_in], 0)
+        L.w_out = torch.zeros(W, L.k_out, dtype=wd, device=dev)
+        L.w_out[:, :k_out] = torch.cat([t.to(device=dev, dtype=wd) for t in cols_out], 1)
+        return L
 
     def weights_fingerprint(self):
         return getattr(self.lm, "_nrl_version", 0)
@@ -205,6 +264,8 @@ class HybridSampler:
         """Re-fuse the arena when the model's weights changed (the optimizer bumps ``_nrl_version``)."""
         if force or self._weights_version != self.weights_fingerprint():
             pools = [(M.k_cache, M.v_cache, M.conv_state, M.state) for L in self.layers for M in L.mixers]
+            self._graphs.clear()                          # captured graphs hold the old arena's addresses
+            self._graph_seen.clear()
             self._build_arena()
             for M, pl in zip([M for L in self.layers for M in L.mixers], pools):
                 M.k_cache, M.v_cache, M.conv_state, M.state = pl
@@ -229,6 +290,11 @@ class HybridSampler:
                 if ms.kind == "window_attention":
                     M.k_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.dim, dtype=wd, device=dev)
                     M.v_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.vdim, dtype=wd, device=dev)
+                elif ms.kind == "conv_attention":
+                    M.k_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.dim, dtype=wd, device=dev)
+                    M.v_cache = torch.zeros(n, ms.kv_heads, self.PAGE, ms.vdim, dtype=wd, device=dev)
+                    ch = ms.heads * ms.dim + ms.kv_heads * (ms.dim + ms.vdim)
+                    M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
                 elif ms.kind == "ssd":
                     ch = ms.heads * ms.vdim + 2 * ms.kv_heads * ms.dim
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
@@ -237,6 +303,8 @@ class HybridSampler:
                     ch = 2 * ms.kv_heads * ms.dim + ms.heads * ms.vdim
                     M.conv_state = torch.zeros(num_slots, ms.conv - 1, ch, **f32)
                     M.state = torch.zeros(num_slots, ms.heads, ms.dim, ms.vdim, **f32)
+        # the last token of every sequence (hashed pair embedding): part of a sequence's state like the convolution taps
+        self.prev_token = torch.zeros(num_slots, dtype=torch.int32, device=dev) if self.stream.pair_buckets else None
         self.num_blocks, self.num_slots = n, num_slots
         self._graphs.clear()                              # captured graphs hold the old pool's addresses
         self._graph_seen.clear()
@@ -310,6 +378,91 @@ class HybridSampler:
         return entry[2]
 
     def _forward(self, plan: StepPlan, rows: List[int]) -> torch.Tensor:
+        if self.stream.kind == "sandwich":
+            return self._forward_sandwich(plan, rows)
+        return self._forward_depth_weighted(plan, rows)
+
+    def _forward_sandwich(self, plan: StepPlan, rows: List[int], keep: Optional[list] = None) -> torch.Tensor:
+        """Stream with a norm before and after every sublayer: ``x += norm_b(gate * sublayer(norm(x)))``.  One fused kernel per
+        sublayer boundary closes the sublayer (gate, post-norm, residual add) and forms the next sublayer's normed input.
+        ``keep``: a list that receives a copy of the stream after every layer."""
+        cfg, dev, wd, st = self.cfg, self.device, self.wdtype, self.stream
+        T, W, eps = plan.T, cfg.width, cfg.norm_eps
+        f32 = dict(dtype=torch.float32, device=dev)
+        x = torch.empty(T, W, **f32)
+        hy.embed_hashed(self.embed, self.pair_table, plan, self.prev_token, st.embed_scale, st.pair_mul_prev, st.pair_mul_cur,
+                        st.pair_buckets, x)
+        h = torch.empty(T, W, dtype=wd, device=dev)
+        ctx: Dict[int, torch.Tensor] = {}                 # values that later layers blend with, by providing layer
+        hy.group_norm_residual(x, None, None, None, None, self.layers[0].w_pre, st.norm_groups, eps, h)
+        for i, L in enumerate(self.layers):
+            U = self._mm(h, L.w_in)                                                   # [T, n_in] float
+            A = (torch.zeros if L.out_pad else torch.empty)(T, L.k_out, dtype=wd, device=dev)
+            for M in L.mixers:
+                out = A[:, M.out_col:M.out_col + M.out_size]
+                if M.spec.kind == "conv_attention":
+                    self._conv_attention(M, U, plan, out, ctx, L.spec.index)
+                elif M.spec.kind == "gated_delta":
+                    self._gated_delta(M, U, plan, eps, out)
+                elif M.spec.kind == "window_attention":
+                    self._window_attention(M, U, plan, eps, out)
+                else:
+                    self._ssd(M, U, plan, eps, out)
+            if L.ff_col is not None:
+                self._feed_forward(L, U, A)
+            o = self._mm(A, L.w_out)                                                  # [T, W] float
+            gate = None
+            if L.gate_col is not None:
+                c, n = L.gate_col
+                gate = U[:, c:c + n]
+            last = i + 1 == len(self.layers)
+            w_next = self.final_gain if last else self.layers[i + 1].w_pre
+            hy.group_norm_residual(x, o, gate, L.gate_bias, L.w_post, w_next, st.norm_groups, eps, h)
+            if keep is not None and (last or self.layers[i + 1].spec.index != L.spec.index):
+                keep.append(x.clone())
+        if not rows:
+            return torch.empty(0, cfg.vocab, **f32)
+        hw = h if rows == list(range(T)) else h[torch.tensor(rows, device=dev)]
+        logits = self._mm(hw.contiguous(), self.head)[:, :cfg.vocab]
+        if st.logit_scale != 1.0:
+            native._count()
+            logits = logits * st.logit_scale
+        return logits
+
+    def _feed_forward(self, L, U, A):
+        spec = L.spec
+        c, n = L.ff_col
+        oc, on = L.ff_out_col
+        if spec.ff_kind == "moe":
+            rc, E = L.router_col
+            hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, gu=U[:, c:c + n], ff=spec.ff, act=A[:, oc:oc + on])
+        else:
+            hy.act_cols(U[:, c:c + n], A[:, oc:oc + on], spec.ff_act)
+
+    def _conv_attention(self, M, U, plan, out, ctx, layer_index):
+        """Biased q / k / v through one short causal convolution (taps carried per slot), values blended with an earlier
+        layer's, keys and values into their pages, then attention with the per-head score terms and output gate."""
+        ms = M.spec
+        T, dev = plan.T, U.device
+        nq, nk, nv = ms.heads * ms.dim, ms.kv_heads * ms.dim, ms.kv_heads * ms.vdim
+        cq, _ = M.cols["q"]
+        qkv = torch.empty(T, nq + nk + nv, dtype=torch.float32, device=dev)
+        hy.causal_conv(U[:, cq:cq + nq + nk + nv], M.vec["conv"], None, M.conv_state, qkv, plan, in_bias=M.vec["in_bias"], act="none")
+        q, k, v = qkv[:, :nq], qkv[:, nq:nq + nk], qkv[:, nq + nk:]
+        other = lam = None
+        if ms.v_blend >= 0 and ms.v_blend != layer_index:
+            other, lam = ctx[ms.v_blend], M.vec["vmix"]
+        hy.kv_write_blend(k, v, other, lam, M.k_cache, M.v_cache, plan)
+        if ms.v_blend == layer_index:
+            ctx[layer_index] = v
+        gate = None
+        if ms.head_gate:
+            cg, ng = M.cols["g"]
+            gate = U[:, cg:cg + ng]
+        hy.window_attention(q, M.k_cache, M.v_cache, plan, ms.window, ms.scale, ms.out_scale, out, chunked=ms.mask == "chunk",
+                            head_scale=M.vec.get("temp"), head_slope=M.vec.get("slope"), gate=gate)
+
+    def _forward_depth_weighted(self, plan: StepPlan, rows: List[int]) -> torch.Tensor:
         cfg, dev, wd = self.cfg, self.device, self.wdtype
         T, W, eps = plan.T, cfg.width, cfg.norm_eps
         f32 = dict(dtype=torch.float32, device=dev)
@@ -333,9 +486,7 @@ class HybridSampler:
                 else:
                     self._gated_delta(M, U, plan, eps, out)
             if L.ff_col is not None:
-                c, n = L.ff_col
-                oc, on = L.ff_out_col
-                hy.act_cols(U[:, c:c + n], A[:, oc:oc + on], "relu2")
+                self._feed_forward(L, U, A)
             o = self._mm(A, L.w_out)                                                  # [T, W] float
             xprev = xcur
         hy.stream_norm(results, nl, o, xprev, self.layers[-1].dw, self.final_gain, eps, xbuf[nl & 1], h, T)
