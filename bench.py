@@ -59,6 +59,9 @@ def parse():
                     help="instead of the GRPO update: prefill / decode throughput of the hybrid step engine (Nezavik) beside the "
                          "Qwen2 engine at equal size, and every new kernel against its roofline (bench/serve_bench.py; one GPU)")
     ap.add_argument("--serve-quick", action="store_true", help="with --serve-bench: one small end-to-end size")
+    ap.add_argument("--serve-model", default="nezavik", choices=["nezavik", "vilosun"],
+                    help="with --serve-bench: nezavik = Nezavik beside Qwen2; vilosun = Vilosun beside Nezavik (same step engine) at "
+                         "equal width and depth, and the kernels Vilosun adds beside Nezavik's like kernels")
     return ap.parse_args()
 
 
@@ -80,7 +83,7 @@ def main():
     if args.serve_bench:
         sys.path.insert(0, os.path.join(ROOT, "bench"))
         import serve_bench
-        serve_bench.main(quick=args.serve_quick)
+        serve_bench.main(quick=args.serve_quick, model=args.serve_model)
         return 0
 
     import torch

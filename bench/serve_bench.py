@@ -1,5 +1,6 @@
 """Serving throughput of the hybrid step engine (Nezavik) beside the paged-KV transformer engine (Qwen2) at equal size,
-plus each new kernel against its roofline and against the like kernel of the transformer path.
+plus each new kernel against its roofline and against the like kernel of the transformer path; with ``--serve-model vilosun``
+the Vilosun family beside Nezavik (same engine) at equal size, and the kernels it adds beside Nezavik's like kernels.
 
 Run through ``python bench.py --serve-bench`` (one GPU).  Random weights, synthetic token ids.  End-to-end numbers go
 through the engines' public ``generate`` (two runs that differ by `new` generated tokens: the difference is `new` decode steps,
@@ -60,6 +61,23 @@ def nezavik_config(width: int, n_layers: int, vocab: int, window: int = 1024, ma
                                     "max_positions": max_positions, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width})
 
 
+def vilosun_config(width: int, n_layers: int, vocab: int, chunk: int = 1024, experts: int = 16, top: int = 2):
+    """Head sizes 128, a quarter as many key/value heads, layer pattern attention / delta / delta / attention; the `top` active
+    experts hold as many weights as the dense 4 x width feed-forward of the model beside it."""
+    from nanorlhf_b200.models.vilosun import VilosunConfig
+    H = width // 128
+    ff = max(128, (8 * width // (3 * top) + 127) // 128 * 128)
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    at = {"type": "attention", "mlp": mlp,
+          "mixer": {"conv": 4, "dim": 128, "vdim": 128, "heads": H, "kv_heads": max(1, H // 4), "mask": {"size": chunk},
+                    "scale": 128 ** -0.5, "v_mix": True}}
+    dl = {"type": "delta", "mlp": mlp, "mixer": {"conv": 4, "dim": 128, "vdim": 128, "heads": H, "kv_heads": H}}
+    pattern = [at, dl, dl, at]
+    return VilosunConfig.from_dict({"architecture": "Vilosun", "layers": [pattern[i % 4] for i in range(n_layers)],
+                                    "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+                                    "logit_scale": 1.0, "norm": {"eps": 1e-6, "groups": 2}, "vocab": vocab, "width": width})
+
+
 def _gen_times(gen, prompts, new, base=4):
     """(prefill seconds, seconds per decode step): generate `base` and `base + new` tokens (median of 3 after a warm-up);
     the difference is `new` decode steps, the rest of the shorter run is the prompt pass."""
@@ -76,6 +94,118 @@ def _gen_times(gen, prompts, new, base=4):
         out.append(sorted(ts)[1])
     step = max(out[1] - out[0], 1e-9) / new
     return max(out[0] - base * step, 1e-9), step
+
+
+def end_to_end_vilosun(width, n_layers, batch, prompt_len, new=128, vocab=32768):
+    """Vilosun beside Nezavik (the closest family: same engine, attention + delta-rule layers) at equal width and depth."""
+    from nanorlhf_b200.models.nezavik import NezavikForCausalLM
+    from nanorlhf_b200.models.vilosun import VilosunForCausalLM
+    from nanorlhf_b200.sampler.hybrid_sampler import HybridSampler
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, vocab - 2, (batch, prompt_len), generator=g).tolist()
+    res = {"width": width, "layers": n_layers, "batch": batch, "prompt_len": prompt_len, "new_tokens": new}
+    for name, make in (("vilosun", lambda: VilosunForCausalLM.from_config(vilosun_config(width, n_layers, vocab), torch.bfloat16, dev, seed=0)),
+                       ("nezavik", lambda: NezavikForCausalLM.from_config(nezavik_config(width, n_layers, vocab), torch.bfloat16, dev, seed=0, rank=64))):
+        model = make()
+        eng = HybridSampler(model, dtype="bf16", max_num_seqs=batch, prefill_token_budget=16384)
+        pre, step = _gen_times(lambda p, mt: eng.generate(p, 1, 1.0, 1.0, mt, None, vocab - 1, 1), prompts, new)
+        res[name] = {"params_m": round(sum(p.numel() for p in model.parameters()) / 1e6, 1),
+                     "prefill_tok_s": round(batch * prompt_len / pre), "decode_tok_s": round(batch / step),
+                     "decode_ms_per_step": round(step * 1e3, 3)}
+        eng.release()
+        del eng, model
+        torch.cuda.empty_cache()
+    return res
+
+
+def kernels_vilosun(width=2048, batch=16, prompt_len=2048, chunk=1024, decode_batch=256, ctx=2048, experts=16, top=2):
+    """The kernels Vilosun adds to the step engine, each beside the like kernel of the Nezavik path."""
+    from nanorlhf_b200 import _C
+    from nanorlhf_b200.ops import hybrid as hy
+    from nanorlhf_b200.sampler.hybrid_sampler import StepPlan
+    hbm, flops_peak, which = _peaks()
+    dev = torch.device("cuda:0")
+    out = {"roofline": which, "width": width}
+    H, Hkv, D = width // 128, max(1, width // 512), 128
+    ff = max(128, (8 * width // (3 * top) + 127) // 128 * 128)
+
+    def plan_for(B, n_new, n_old):
+        s = _C.StepScheduler((n_old + n_new + 15) // 16 * B + 8, 16, B)
+        sids = [s.open() for _ in range(B)]
+        if n_old:
+            s.plan(sids, [n_old] * B)
+        data, E, T, MB = s.plan(sids, [n_new] * B)
+        return StepPlan(torch.from_numpy(data).to(dev), E, T, MB), s
+
+    def report(name, sec, bytes_, flops=0.0):
+        floor = max(bytes_ / hbm, flops / flops_peak)
+        out[name] = {"us": round(sec * 1e6, 1), "gb_s": round(bytes_ / sec / 1e9, 1), "tflop_s": round(flops / sec / 1e12, 2),
+                     "roofline_frac": round(floor / sec, 3)}
+
+    for phase, B, n_new, n_old in (("prefill", batch, prompt_len, 0), ("decode", decode_batch, 1, ctx - 1)):
+        plan, sched = plan_for(B, n_new, n_old)
+        T = plan.T
+        f32 = dict(dtype=torch.float32, device=dev)
+        plan.tokens.copy_(torch.randint(0, 32000, (T,), dtype=torch.int32, device=dev))
+        # -- embeddings
+        emb, pair = torch.randn(32768, width, device=dev).bfloat16(), torch.randn(65522, width, device=dev).bfloat16()
+        prev, x0 = torch.zeros(B, dtype=torch.int32, device=dev), torch.empty(T, width, **f32)
+        sec = _time(lambda: hy.embed_hashed(emb, pair, plan, prev, 1.0, 31, 17, 65521, x0))
+        report(f"{phase}.embed_hashed", sec, T * width * 8.0)
+        pos_t = torch.randn(8192, width, device=dev).bfloat16()
+        sec = _time(lambda: hy.embed_pos(emb, pos_t, plan.tokens, plan.pos, x0))
+        report(f"{phase}.nezavik.embed_pos", sec, T * width * 8.0)
+        # -- sublayer boundary: gate, post-norm, residual, next pre-norm vs the depth-weighted boundary at depth 1
+        x, o, gate = torch.randn(T, width, **f32), torch.randn(T, width, **f32), torch.randn(T, width, **f32)
+        gb, wa, wb = torch.randn(width, **f32), torch.ones(width, **f32), torch.ones(width, **f32)
+        h = torch.empty(T, width, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.group_norm_residual(x, o, gate, gb, wa, wb, 2, 1e-6, h))
+        report(f"{phase}.group_norm_residual", sec, T * width * (4.0 * 4 + 2))
+        results = torch.randn(2, T, width, **f32)
+        xc, dw, gain = torch.empty(T, width, **f32), torch.rand(2, **f32), torch.ones(1, **f32)
+        sec = _time(lambda: hy.stream_norm(results, 1, o, x, dw, gain, 1e-6, xc, h, T))
+        report(f"{phase}.nezavik.stream_norm(depth 1)", sec, T * width * (4.0 * 5 + 2))
+        # -- attention: convolution, page write, chunked attention vs q/k norm + page write, sliding-window attention
+        nq, nk = H * D, Hkv * D
+        raw, cw, cb = torch.randn(T, nq + 2 * nk, **f32), torch.randn(nq + 2 * nk, 4, **f32), torch.randn(nq + 2 * nk, **f32)
+        cst, qkv = torch.zeros(B, 3, nq + 2 * nk, **f32), torch.empty(T, nq + 2 * nk, **f32)
+        sec = _time(lambda: hy.causal_conv(raw, cw, None, cst, qkv, plan, in_bias=cb, act="none"))
+        report(f"{phase}.causal_conv(qkv, biased)", sec, T * (nq + 2 * nk) * 8.0 + B * 3 * (nq + 2 * nk) * 8.0)
+        kc = torch.randn(sched.num_free_blocks() + plan.max_blocks * B + 8, Hkv, 16, D, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        q, k, v = qkv[:, :nq], qkv[:, nq:nq + nk], qkv[:, nq + nk:]
+        vo, lam = torch.randn(T, nk, **f32), torch.full((1,), 0.3, **f32)
+        sec = _time(lambda: hy.kv_write_blend(k, v, vo, lam, kc, vc, plan))
+        report(f"{phase}.kv_write_blend", sec, T * nk * (4.0 * 4 + 2 * 2))
+        qw_, kw_ = torch.ones(D, **f32), torch.ones(D, **f32)
+        sec = _time(lambda: hy.qknorm_kv_write(q, k, v, qw_, kw_, 1e-6, kc, vc, plan))
+        report(f"{phase}.nezavik.qknorm_kv_write", sec, T * (H + 2 * Hkv) * D * 4.0 + T * H * D * 4.0 + T * 2 * Hkv * D * 2.0)
+        ao = torch.empty(T, H * D, dtype=torch.bfloat16, device=dev)
+        temp, slope, hg = torch.rand(H, **f32) + 0.5, torch.rand(H, **f32) * 0.1, torch.randn(T, H, **f32)
+        if phase == "prefill":
+            keys_c = sum(p % chunk + 1 for p in range(n_new)) * B
+            keys_w = sum(min(p + 1, chunk) for p in range(n_new)) * B
+        else:
+            keys_c, keys_w = ((ctx - 1) % chunk + 1) * B, min(ctx, chunk) * B
+        byt = lambda keys: (T * H * D * 6.0 + T * 2 * Hkv * D * 2.0) if phase == "prefill" else (keys * 2 * Hkv * D * 2.0 + T * H * D * 6.0)
+        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, chunk, D ** -0.5, 1.0, ao, chunked=True, head_scale=temp,
+                                                head_slope=slope, gate=hg), iters=3, warm=1)
+        report(f"{phase}.chunk_attention(c={chunk})", sec, byt(keys_c), flops=4.0 * keys_c * H * D)
+        sec = _time(lambda: hy.window_attention(q, kc, vc, plan, chunk, D ** -0.5, 1.0, ao), iters=3, warm=1)
+        report(f"{phase}.nezavik.window_attention(w={chunk})", sec, byt(keys_w), flops=4.0 * keys_w * H * D)
+        del kc, vc
+        # -- feed-forward: routing + expert activations vs the dense squared-ReLU activation
+        U = torch.randn(T, experts + experts * 2 * ff, **f32)
+        A = torch.empty(T, experts * ff, dtype=torch.bfloat16, device=dev)
+        rb = torch.zeros(experts, **f32)
+        sec = _time(lambda: hy.moe_route(U[:, :experts], rb, top, gu=U[:, experts:], ff=ff, act=A))
+        report(f"{phase}.moe_route(dense form, {experts} experts top {top})", sec, T * (experts * 4.0 + top * ff * 8.0 + experts * ff * 2.0))
+        up = torch.randn(T, 4 * width, **f32)
+        ub = torch.empty(T, 4 * width, dtype=torch.bfloat16, device=dev)
+        sec = _time(lambda: hy.act_cols(up, ub, "relu2"))
+        report(f"{phase}.nezavik.relu2", sec, T * 4 * width * 6.0)
+    return out
 
 
 def end_to_end(width, n_layers, batch, prompt_len, new=128, vocab=32768):
@@ -225,11 +355,23 @@ def kernels(width=2048, batch=16, prompt_len=2048, window=1024, decode_batch=256
     return out
 
 
-def main(quick: bool = False, small: bool = False):
+def main(quick: bool = False, small: bool = False, model: str = "nezavik"):
     from nanorlhf_b200.ops import native
+    global SMALL
     native.load()
+    if model == "vilosun":
+        SMALL = small
+        if small:
+            print(json.dumps({"bench": "serve-vilosun-small",
+                              "kernels": kernels_vilosun(width=1024, batch=8, prompt_len=1024, decode_batch=64, ctx=1024)}))
+            return None
+        res = {"bench": "serve-vilosun", "kernels": kernels_vilosun(), "end_to_end": []}
+        for width, layers, batch, plen in ((1024, 8, 32, 1024), (2048, 8, 16, 2048)) if not quick else ((1024, 4, 8, 512),):
+            res["end_to_end"].append(end_to_end_vilosun(width, layers, batch, plen))
+        res["gpu_launches"] = native.launches()
+        print(json.dumps(res))
+        return res
     if small:                                  # kernels only, on a case of a few hundred MB
-        global SMALL
         SMALL = True
         print(json.dumps({"bench": "serve-small", "kernels": kernels(width=1024, batch=8, prompt_len=1024, decode_batch=64, ctx=1024)}))
         return None
@@ -242,4 +384,4 @@ def main(quick: bool = False, small: bool = False):
 
 
 if __name__ == "__main__":
-    main(quick="--quick" in sys.argv, small="--small" in sys.argv)
+    main(quick="--quick" in sys.argv, small="--small" in sys.argv, model="vilosun" if "--vilosun" in sys.argv else "nezavik")

@@ -436,14 +436,13 @@ cudaError_t nrl_window_attention(const float* q, long sq, const void* k_cache, c
   if (Dv > 32 * kMaxDvPerLane || Hq % Hkv != 0 || window < 1 || cache_f32 != out_f32) return cudaErrorInvalidValue;
   NrlAttnMods md = {0, nullptr, nullptr, nullptr, 0};
   if (mods != nullptr) md = *mods;
-  const bool plain = !md.chunked && md.head_scale == nullptr && md.head_slope == nullptr && md.gate == nullptr;
   // prompt portions over bf16 pages: tensor cores
-  if (plain && (impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page)) {
+  if ((impl == 0 || impl == 3) && !cache_f32 && nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page)) {
     if (single_token && nsplit >= 1 && part != nullptr)
       return nrl_window_attention_decode(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out,
-                                         so, T, Hq, Hkv, D, Dv, page, nsplit, part, s);
+                                         so, T, Hq, Hkv, D, Dv, page, nsplit, part, &md, s);
     return nrl_window_attention_mma(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so,
-                                    T, Hq, Hkv, D, Dv, page, single_token, s);
+                                    T, Hq, Hkv, D, Dv, page, single_token, &md, s);
   }
   if (impl == 3) return cudaErrorInvalidValue;
   if (impl != 2 && Dv <= 128 && Dv % 4 == 0 && D <= 512) {

@@ -1,4 +1,5 @@
-// Sliding-window attention on the tensor cores, reading the 16-token bf16 pages in place.
+// Sliding-window (or chunked) attention on the tensor cores, reading the 16-token bf16 pages in place.  The optional terms of
+// NrlAttnMods (chunk mask, per-head score multiplier and distance slope, per-head output gate) are applied in float.
 //
 // Prompt portions (window_attention_mma_kernel): a block owns 64 query rows that share one key/value head -- QT
 // consecutive tokens x HB query heads -- as four warps of 16 rows, and walks the keys its rows can see in blocks of 64
@@ -57,6 +58,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// first key a query at position p sees (window form: not clamped at 0, callers compare or clamp)
+__device__ __forceinline__ int first_key(int p, int window, int chunked) { return chunked ? p - p % window : p - window + 1; }
+__device__ __forceinline__ float sigmoid_(float z) { return 1.f / (1.f + expf(-z)); }
+
 __device__ __forceinline__ int sel4(const int (&v)[4], int i) { return i == 0 ? v[0] : i == 1 ? v[1] : i == 2 ? v[2] : v[3]; }
 
 // the four pages that hold keys kb .. kb + 63 of a sequence (0 where the sequence ends before)
@@ -89,7 +94,8 @@ __global__ void __launch_bounds__(kThreads, 3)
 window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
                             const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                             const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale, float out_scale,
-                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT) {
+                            __nv_bfloat16* __restrict__ out, long so, int T, int Hq, int Hkv, int D, int Dv, int HB, int QT,
+                            NrlAttnMods md) {
   constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [2][kBN][LDK]
@@ -132,7 +138,15 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
 #pragma unroll
   for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // running maxima live in the log2 domain
-  const float sl2 = scale * 1.4426950408889634f;
+  // per row (= per query head): score multiplier and distance slope, both in the log2 domain
+  float sl2[2], slr[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int hq = min(h0 + (w * 16 + gq + hf * 8) % HB, Hq - 1);
+    sl2[hf] = scale * 1.4426950408889634f * (md.head_scale != nullptr ? md.head_scale[hq] : 1.f);
+    slr[hf] = md.head_slope != nullptr ? md.head_slope[hq] * 1.4426950408889634f : 0.f;
+  }
+  const bool sloped = md.head_slope != nullptr;
 
   int t = t_begin;
   while (t < t_end) {
@@ -140,23 +154,25 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     int tn = t + 1;
     while (tn < t_end && tok_entry[tn] == e) ++tn;
     const int p_first = pos[t];
-    const int lo = max(0, p_first - window + 1), hi = p_first + (tn - t) - 1;
+    const int lo = max(0, first_key(p_first, window, md.chunked)), hi = p_first + (tn - t) - 1;
     const int* bt = block_table + static_cast<long>(e) * max_blocks;
     const int kb0 = (lo / kBN) * kBN;
     const int nblk = (hi - kb0) / kBN + 1;
     // positions of this thread's rows inside the run (or "not in this run")
-    int pq[2];
+    int pq[2], plo[2];
     bool act[2];
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       act[hf] = row_ok[hf] && row_t[hf] >= t && row_t[hf] < tn;
       pq[hf] = p_first + (row_t[hf] - t);
+      plo[hf] = first_key(pq[hf], window, md.chunked);
     }
     // keys the warp's rows of this run can see: [wlo, whi]
     const int wa = max(wt_lo, t), wb = min(wt_hi, tn - 1);
     const bool warp_in = wa <= wb;
     const bool warp_full = wt_lo >= t && wt_hi < tn;       // every row of the warp that holds a query belongs to this run
-    const int whi = p_first + (wb - t), wlo = p_first + (wa - t) - window + 1;
+    const int whi = p_first + (wb - t), wlo = first_key(p_first + (wa - t), window, md.chunked);
+    const int whi_lo = first_key(whi, window, md.chunked);  // first key of the warp's last row: blocks from here on are seen by all
 
     __syncthreads();                                       // the previous run's last block has been consumed
     int pg[4];
@@ -198,14 +214,14 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
           }
         }
         // scale (log2 domain), mask, online softmax (float).  A block that every row of the warp sees whole needs no mask.
-        const bool interior = warp_full && kb + kBN - 1 <= p_first + (wt_lo - t) && kb > whi - window;
+        const bool interior = !sloped && warp_full && kb + kBN - 1 <= p_first + (wt_lo - t) && kb >= whi_lo;
         float mx[2] = {-INFINITY, -INFINITY};
         if (interior) {
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              s[n][i] *= sl2;
+              s[n][i] *= sl2[i >> 1];
               mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
             }
           }
@@ -215,8 +231,8 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int hf = i >> 1, j = kb + n * 8 + 2 * tq + (i & 1);
-              const bool valid = act[hf] && j <= pq[hf] && j > pq[hf] - window;
-              const float sc = valid ? s[n][i] * sl2 : -INFINITY;
+              const bool valid = act[hf] && j <= pq[hf] && j >= plo[hf];
+              const float sc = valid ? s[n][i] * sl2[hf] - slr[hf] * static_cast<float>(pq[hf] - j) : -INFINITY;
               s[n][i] = sc;
               mx[hf] = fmaxf(mx[hf], sc);
             }
@@ -280,7 +296,8 @@ window_attention_mma_kernel(const float* __restrict__ q, long sq, const __nv_bfl
     if (!row_ok[hf]) continue;
     const int r = w * 16 + gq + hf * 8;
     __nv_bfloat16* dst = out + static_cast<long>(row_t[hf]) * so + static_cast<long>(h0 + r % HB) * Dv;
-    const float f = out_scale / l;
+    float f = out_scale / l;
+    if (md.gate != nullptr) f *= sigmoid_(md.gate[static_cast<long>(row_t[hf]) * md.gate_stride + h0 + r % HB]);
 #pragma unroll
     for (int i = 0; i < 2 * NV; ++i) {
       const int c = i * 8 + 2 * tq;
@@ -302,7 +319,7 @@ __global__ void __launch_bounds__(kThreads)
 window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_bfloat16* __restrict__ k_cache,
                                const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                                const int* __restrict__ tok_entry, const int* __restrict__ pos, int window, float scale,
-                               float* __restrict__ part, int Hq, int Hkv, int D, int Dv, int nsplit) {
+                               float* __restrict__ part, int Hq, int Hkv, int D, int Dv, int nsplit, NrlAttnMods md) {
   constexpr int DP = 16 * KS, DVP = 16 * NV, LDK = DP + kPad, LDV = DVP + kPad;
   constexpr int kStageElems = 16 * LDK + 16 * LDV;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -327,7 +344,7 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
     for (int ks = 0; ks < KS; ++ks) ldsm_x4(smem_u32(sQ + rr * LDK + ks * 16 + (m >> 1) * 8), qf[ks]);
   }
   const int p = pos[t];
-  const int lo = max(0, p - window + 1);
+  const int lo = max(0, first_key(p, window, md.chunked));
   const int* bt = block_table + static_cast<long>(tok_entry[t]) * max_blocks;
   const int pg_first = lo >> 4, npages = (p >> 4) - pg_first + 1;
   const int per_part = (npages + nparts - 1) / nparts;
@@ -358,7 +375,13 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
 #pragma unroll
   for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  const float sl2 = scale * 1.4426950408889634f;
+  float sl2[2], slr[2];                                    // per row (= query head), log2 domain
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int hq = min(h0 + gq + hf * 8, Hq - 1);
+    sl2[hf] = scale * 1.4426950408889634f * (md.head_scale != nullptr ? md.head_scale[hq] : 1.f);
+    slr[hf] = md.head_slope != nullptr ? md.head_slope[hq] * 1.4426950408889634f : 0.f;
+  }
 #pragma unroll
   for (int i = 0; i < kDecStages - 1; ++i) {
     if (pg0 + i < pg1) load_page(i, pg0 + i);
@@ -390,7 +413,7 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int j = pg * 16 + n * 8 + 2 * tq + (i & 1);
-        const float sc = (j <= p && j >= lo) ? s[n][i] * sl2 : -INFINITY;
+        const float sc = (j <= p && j >= lo) ? s[n][i] * sl2[i >> 1] - slr[i >> 1] * static_cast<float>(p - j) : -INFINITY;
         s[n][i] = sc;
         mrow[i >> 1] = fmaxf(mrow[i >> 1], sc);
       }
@@ -463,9 +486,10 @@ window_attention_decode_kernel(const float* __restrict__ q, long sq, const __nv_
 
 // block per (token, query head): out = out_scale * sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s
 __global__ void window_attention_merge_kernel(const float* __restrict__ part, int nsplit, int Hq, int Dv, float out_scale,
-                                              __nv_bfloat16* __restrict__ out, long so) {
+                                              __nv_bfloat16* __restrict__ out, long so, const float* __restrict__ gate, long gate_stride) {
   const long t = blockIdx.x;
   const int h = blockIdx.y;
+  if (gate != nullptr) out_scale *= sigmoid_(gate[t * gate_stride + h]);
   const float* p = part + (t * Hq + h) * nsplit * (Dv + 2);
   float M = -INFINITY;
   for (int x = 0; x < nsplit; ++x) M = fmaxf(M, p[x * (Dv + 2) + Dv]);
@@ -487,7 +511,7 @@ __global__ void window_attention_merge_kernel(const float* __restrict__ part, in
 template <int KS, int NV>
 cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                    const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T, int Hq,
-                   int Hkv, int D, int Dv, int single_token, cudaStream_t s) {
+                   int Hkv, int D, int Dv, int single_token, const NrlAttnMods& md, cudaStream_t s) {
   const int per_g = Hq / Hkv;
   // a step of single tokens that the per-warp kernel does not take: one token per block
   const int HB = per_g < kBM ? per_g : kBM, QT = single_token ? 1 : kBM / HB;
@@ -503,14 +527,14 @@ cudaError_t launch(const float* q, long sq, const void* k_cache, const void* v_c
   const dim3 grid((T + QT - 1) / QT, Hkv, (per_g + HB - 1) / HB);
   kern<<<grid, kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
                                     block_table, max_blocks, tok_entry, pos, window, scale, out_scale, static_cast<__nv_bfloat16*>(out), so,
-                                    T, Hq, Hkv, D, Dv, HB, QT);
+                                    T, Hq, Hkv, D, Dv, HB, QT, md);
   return cudaGetLastError();
 }
 
 template <int KS, int NV>
 cudaError_t launch_decode(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                           const int* tok_entry, const int* pos, int window, float scale, float out_scale, void* out, long so, int T,
-                          int Hq, int Hkv, int D, int Dv, int nsplit, float* part, cudaStream_t s) {
+                          int Hq, int Hkv, int D, int Dv, int nsplit, float* part, const NrlAttnMods& md, cudaStream_t s) {
   constexpr size_t smem = sizeof(__nv_bfloat16) * (16 * (16 * KS + kPad) +
                                                    4 * kDecStages * (16 * (16 * KS + kPad) + 16 * (16 * NV + kPad)));
   auto kern = window_attention_decode_kernel<KS, NV>;
@@ -522,11 +546,12 @@ cudaError_t launch_decode(const float* q, long sq, const void* k_cache, const vo
   }
   kern<<<dim3(T, Hkv, nsplit), kThreads, smem, s>>>(q, sq, static_cast<const __nv_bfloat16*>(k_cache),
                                                     static_cast<const __nv_bfloat16*>(v_cache), block_table, max_blocks, tok_entry, pos,
-                                                    window, scale, part, Hq, Hkv, D, Dv, nsplit);
+                                                    window, scale, part, Hq, Hkv, D, Dv, nsplit, md);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   window_attention_merge_kernel<<<dim3(T, Hq), Dv <= 32 ? 32 : Dv <= 64 ? 64 : 128, 0, s>>>(part, nsplit * 4, Hq, Dv, out_scale,
-                                                                                          static_cast<__nv_bfloat16*>(out), so);
+                                                                                          static_cast<__nv_bfloat16*>(out), so, md.gate,
+                                                                                          md.gate_stride);
   return cudaGetLastError();
 }
 
@@ -539,15 +564,17 @@ extern "C" {
 cudaError_t nrl_window_attention_decode(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                         int max_blocks, const int* tok_entry, const int* pos, int window, float scale,
                                         float out_scale, void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page,
-                                        int nsplit, float* part, cudaStream_t s) {
+                                        int nsplit, float* part, const NrlAttnMods* mods, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
+  NrlAttnMods md = {0, nullptr, nullptr, nullptr, 0};
+  if (mods != nullptr) md = *mods;
   if (!nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) || Hq / Hkv > 16 || window < 1 || nsplit < 1 || part == nullptr)
     return cudaErrorInvalidValue;
   const int ks = D <= 32 ? 2 : D <= 64 ? 4 : 8, nv = Dv <= 32 ? 2 : Dv <= 64 ? 4 : 8;
 #define NRL_WD(KS_, NV_)                                                                                                         \
   if (ks == KS_ && nv == NV_)                                                                                                    \
     return launch_decode<KS_, NV_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so, \
-                                   T, Hq, Hkv, D, Dv, nsplit, part, s);
+                                   T, Hq, Hkv, D, Dv, nsplit, part, md, s);
   NRL_WD(2, 2) NRL_WD(2, 4) NRL_WD(2, 8) NRL_WD(4, 2) NRL_WD(4, 4) NRL_WD(4, 8) NRL_WD(8, 2) NRL_WD(8, 4) NRL_WD(8, 8)
 #undef NRL_WD
   return cudaErrorInvalidValue;
@@ -573,14 +600,16 @@ int nrl_window_attention_mma_fits(const void* out, long so, int Hq, int Hkv, int
 cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
-                                     cudaStream_t s) {
+                                     const NrlAttnMods* mods, cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
+  NrlAttnMods md = {0, nullptr, nullptr, nullptr, 0};
+  if (mods != nullptr) md = *mods;
   if (!nrl_window_attention_mma_fits(out, so, Hq, Hkv, D, Dv, page) || window < 1) return cudaErrorInvalidValue;
   const int ks = D <= 32 ? 2 : D <= 64 ? 4 : 8, nv = Dv <= 32 ? 2 : Dv <= 64 ? 4 : 8;
 #define NRL_WM(KS_, NV_)                                                                                                         \
   if (ks == KS_ && nv == NV_)                                                                                                    \
     return launch<KS_, NV_>(q, sq, k_cache, v_cache, block_table, max_blocks, tok_entry, pos, window, scale, out_scale, out, so, T, Hq, \
-                            Hkv, D, Dv, single_token, s);
+                            Hkv, D, Dv, single_token, md, s);
   NRL_WM(2, 2) NRL_WM(2, 4) NRL_WM(2, 8) NRL_WM(4, 2) NRL_WM(4, 4) NRL_WM(4, 8) NRL_WM(8, 2) NRL_WM(8, 4) NRL_WM(8, 8)
 #undef NRL_WM
   return cudaErrorInvalidValue;

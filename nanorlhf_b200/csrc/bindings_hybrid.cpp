@@ -5,7 +5,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "gemm_tc.h"
 #include "hybrid_kernels.h"
+#include "tma_host.h"
 
 namespace {
 
@@ -192,11 +194,10 @@ void window_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
     md.gate = f32(*gate, "gate");
     md.gate_stride = gate->stride(0);
   }
-  const bool plain = !chunked && md.head_scale == nullptr && md.head_slope == nullptr && md.gate == nullptr;
   // steps of single tokens on bf16 pages: cut the key walk into parts so that few sequences still fill the GPU
   int nsplit = 0;
   Tensor part;
-  if (plain && single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
+  if (single_token && (impl == 0 || impl == 3) && k_cache.scalar_type() == at::kBFloat16 &&
       nrl_window_attention_mma_fits(out.data_ptr(), out.stride(0), Hq, Hkv, D, Dv, page)) {
     nsplit = nrl_window_attention_splits(T, Hq, Hkv, static_cast<int>(window), static_cast<int>(block_table.size(1)), page);
     if (nsplit >= 1) part = at::empty({T, Hq, 4 * nsplit, Dv + 2}, q.options().dtype(at::kFloat));
@@ -289,10 +290,92 @@ void moe_route(const Tensor& router, const c10::optional<Tensor>& router_bias, i
         "moe_route");
 }
 
+// ---- mixture of experts, grouped form ----
+std::vector<Tensor> moe_plan(const Tensor& ids, int64_t E, int64_t tile_rows) {
+  c10::cuda::CUDAGuard guard(ids.device());
+  TORCH_CHECK(ids.dim() == 2 && ids.scalar_type() == torch::kInt32 && ids.is_contiguous(), "moe_plan: ids int32 [T, top]");
+  const int R = static_cast<int>(ids.numel()), top = static_cast<int>(ids.size(1));
+  const int64_t max_tiles = (R + tile_rows - 1) / tile_rows + E;
+  auto opt = ids.options();
+  Tensor slot_of = at::empty({R}, opt), row_token = at::empty({R}, opt), seg = at::empty({E + 1}, opt);
+  Tensor tiles = at::zeros({max_tiles, 3}, opt), num_tiles = at::zeros({1}, opt);
+  check(nrl_moe_plan(i32(ids, "ids"), R, top, static_cast<int>(E), static_cast<int>(tile_rows), slot_of.data_ptr<int>(),
+                     row_token.data_ptr<int>(), seg.data_ptr<int>(), tiles.data_ptr<int>(), num_tiles.data_ptr<int>(), cur_stream()),
+        "moe_plan");
+  return {slot_of, row_token, seg, tiles, num_tiles};
+}
+
+void gather_rows(const Tensor& in, const Tensor& row_token, Tensor out) {
+  c10::cuda::CUDAGuard guard(in.device());
+  TORCH_CHECK(in.dim() == 2 && out.dim() == 2 && in.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16 &&
+                  in.stride(1) == 1 && out.is_contiguous() && out.size(1) == in.size(1) && out.size(0) == row_token.numel(),
+              "gather_rows: bf16 in [T, W], out [R, W] contiguous");
+  check(nrl_gather_rows16(in.data_ptr(), in.stride(0), i32(row_token, "row_token"), out.data_ptr(), static_cast<int>(out.size(0)),
+                          static_cast<int>(in.size(1)), cur_stream()),
+        "gather_rows");
+}
+
+void swiglu_rows(const Tensor& gu, Tensor act) {
+  c10::cuda::CUDAGuard guard(gu.device());
+  TORCH_CHECK(gu.dim() == 2 && act.dim() == 2 && act.scalar_type() == torch::kBFloat16 && act.stride(1) == 1 && gu.size(0) == act.size(0) &&
+                  gu.size(1) == 2 * act.size(1), "swiglu_rows: gu float [R, 2 ff], act bf16 [R, ff]");
+  check(nrl_swiglu_rows(f32(gu, "gu"), gu.stride(0), act.data_ptr(), act.stride(0), static_cast<int>(gu.size(0)),
+                        static_cast<int>(act.size(1)), cur_stream()),
+        "swiglu_rows");
+}
+
+void moe_combine(const Tensor& y, const Tensor& slot_of, const Tensor& wts, Tensor out) {
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(y.dim() == 2 && out.dim() == 2 && wts.dim() == 2 && wts.is_contiguous() && out.size(0) == wts.size(0) &&
+                  out.size(1) == y.size(1) && slot_of.numel() == wts.numel() && y.size(0) == wts.numel(), "moe_combine: shapes");
+  check(nrl_moe_combine(f32(y, "y"), y.stride(0), i32(slot_of, "slot_of"), f32(wts, "wts"), static_cast<int>(wts.size(1)),
+                        f32w(out, "out"), out.stride(0), static_cast<int>(out.size(0)), static_cast<int>(out.size(1)), cur_stream()),
+        "moe_combine");
+}
+
+// out[r, :] = a[r, :] . b[expert(r)]^T for rows sorted by expert: a bf16 [R, K], b bf16 [E * N, K], out float [R, N];
+// tiles / num_tiles from moe_plan (128-row tiles).
+void gemm_tc_grouped(const Tensor& a, const Tensor& b, Tensor out, const Tensor& tiles, const Tensor& num_tiles, int64_t block_n) {
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && a.dim() == 2 &&
+                  b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_tc_grouped: bf16 2D operands with unit inner stride");
+  TORCH_CHECK((a.stride(0) * 2) % 16 == 0 && (b.stride(0) * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "gemm_tc_grouped: 16-byte aligned rows");
+  const int64_t R = a.size(0), K = a.size(1), N = out.size(1);
+  TORCH_CHECK(b.size(1) == K && K % 8 == 0 && N % 8 == 0 && b.size(0) % N == 0, "gemm_tc_grouped: b [E * N, K], K and N multiples of 8");
+  TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.dim() == 2 && out.size(0) == R && out.stride(1) == 1 && out.stride(0) % 4 == 0 &&
+                  (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "gemm_tc_grouped: out float [R, N], 16-byte aligned rows");
+  TORCH_CHECK(tiles.scalar_type() == torch::kInt32 && tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 3 &&
+                  num_tiles.scalar_type() == torch::kInt32 && num_tiles.numel() == 1, "gemm_tc_grouped: tile table");
+  if (R == 0) return;
+  const int bn = block_n > 0 ? static_cast<int>(block_n) : (N <= 64 ? 64 : 128);
+  const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap maps[2];
+  maps[0] = nrl::make_tma_2d(a.data_ptr(), a.size(0), a.size(1), a.stride(0) * 2, 128, 64, BF, 2);
+  maps[1] = nrl::make_tma_2d(b.data_ptr(), b.size(0), b.size(1), b.stride(0) * 2, bn, 64, BF, 2);
+  nrl::tc::TcParams p{};
+  p.M = static_cast<int>(R); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.K2 = 0;
+  p.alpha = 1.f;
+  p.out_f32 = out.data_ptr<float>();
+  p.out_f32_stride = out.stride(0);
+  p.grp_tiles = tiles.data_ptr<int>();
+  p.grp_num_tiles = num_tiles.data_ptr<int>();
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  check(nrl_gemm_tc_grouped(maps, &p, bn, static_cast<int>(tiles.size(0)), sms, cur_stream()), "gemm_tc_grouped");
+}
+
 }  // namespace
 
 namespace nrl {
 void bind_hybrid(pybind11::module_& m) {
+  m.def("moe_plan", &moe_plan, "sort (token, choice) pairs by expert: slot_of, row_token, seg, tiles, num_tiles");
+  m.def("gather_rows", &gather_rows, "out[r] = in[row_token[r]] (bf16 rows)");
+  m.def("swiglu_rows", &swiglu_rows, "act = silu(gu[:, :ff]) * gu[:, ff:] (float in, bf16 out)");
+  m.def("moe_combine", &moe_combine, "out[t] = sum_k wts[t, k] y[slot_of[t, k]]");
+  m.def("gemm_tc_grouped", &gemm_tc_grouped, "grouped tcgen05 GEMM over rows sorted by expert, float32 out", pybind11::arg("a"),
+        pybind11::arg("b"), pybind11::arg("out"), pybind11::arg("tiles"), pybind11::arg("num_tiles"), pybind11::arg("block_n") = 0);
   m.def("embed_pos", &embed_pos, "x0 = embed[tok] + pos_table[pos] (float)");
   m.def("stream_norm", &stream_norm, "close a layer, form the depth-weighted stream and its single-gain RMS norm");
   m.def("act_cols", &act_cols, "typed out = act(float in): 0 copy, 1 relu^2");

@@ -180,7 +180,7 @@ NRL_DEVICE void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0,
 // FP8: A and B are e4m3 bytes, K-major (a 128-byte swizzle row = 128 contraction elements), the MMA is kind::f8f6f4
 // (K = 32 per instruction, twice the bf16 rate) and the epilogue applies the per-row (token) and per-column (output
 // channel) dequantisation scales -- the sampler's fp8 rollout GEMMs (north star: fp8 tcgen05 GEMM in the decoder).
-template <int CG, int BN, bool A_MN, bool B_MN, int EPI, bool SPLIT = false, bool BATCH = false, bool FP8 = false>
+template <int CG, int BN, bool A_MN, bool B_MN, int EPI, bool SPLIT = false, bool BATCH = false, bool FP8 = false, bool GROUPED = false>
 NRL_DEVICE void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, const CUtensorMap& tmB2,
                              const CUtensorMap& tmD, const TcParams& p) {
   using C = Cfg<CG, BN, B_MN>;
@@ -203,7 +203,8 @@ NRL_DEVICE void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB, con
   const int kb_per_split = (num_kb + splits - 1) / splits;
   const int tiles_per_batch = num_m * num_n;
   // SPLIT: work item = (tile, k-range), splits of a tile adjacent.  BATCH: work item = (batch, tile), third TMA coordinate
-  const int num_work = tiles_per_batch * (BATCH ? p.batch : splits);
+  // GROUPED: work item = (row tile of the device-side table, column block); the column blocks of a row tile are adjacent
+  const int num_work = GROUPED ? __ldg(p.grp_num_tiles) * num_n : tiles_per_batch * (BATCH ? p.batch : splits);
   const int unit = blockIdx.x / CG, num_units = gridDim.x / CG;
   volatile int* s_last = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
@@ -244,9 +245,15 @@ NRL_DEVICE void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB, con
       uint32_t phase = 0;
       for (int w = unit; w < num_work; w += num_units) {
         const int bidx = BATCH ? w / tiles_per_batch : 0;
-        const TileCoord c = tile_coord(BATCH ? w % tiles_per_batch : w / splits, num_m, num_n);
-        const int m0 = (c.m_tile * CG + static_cast<int>(rank)) * BLOCK_M;
-        const int n0 = c.n_blk * BN + static_cast<int>(rank) * C::kBRows;
+        TileCoord c = GROUPED ? TileCoord{0, 0} : tile_coord(BATCH ? w % tiles_per_batch : w / splits, num_m, num_n);
+        int m0 = (c.m_tile * CG + static_cast<int>(rank)) * BLOCK_M;
+        int n0 = c.n_blk * BN + static_cast<int>(rank) * C::kBRows;
+        if (GROUPED) {
+          const int mt = w / num_n;
+          c.n_blk = w - mt * num_n;
+          m0 = __ldg(p.grp_tiles + 3 * mt + 1);
+          n0 = __ldg(p.grp_tiles + 3 * mt) * p.N + c.n_blk * BN;      // the expert's block of B rows
+        }
         const int kb_lo = BATCH ? 0 : (w % splits) * kb_per_split, kb_hi = BATCH ? num_kb : min(num_kb, kb_lo + kb_per_split);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           mbar_wait(&empty_bar[stage], phase ^ 1);
@@ -330,10 +337,16 @@ NRL_DEVICE void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB, con
       const int tile_id = BATCH ? w % tiles_per_batch : w / splits;
       const int bidx = BATCH ? w / tiles_per_batch : 0;
       (void)bidx;
-      const TileCoord c = tile_coord(tile_id, num_m, num_n);
+      TileCoord c = GROUPED ? TileCoord{0, 0} : tile_coord(tile_id, num_m, num_n);
       const int m_blk = c.m_tile * CG + static_cast<int>(rank);
-      const int row = m_blk * BLOCK_M + row_in_tile;
-      const bool row_ok = row < p.M;
+      int row = m_blk * BLOCK_M + row_in_tile;
+      bool row_ok = row < p.M;
+      if (GROUPED) {
+        const int mt = w / num_n;
+        c.n_blk = w - mt * num_n;
+        row = __ldg(p.grp_tiles + 3 * mt + 1) + row_in_tile;
+        row_ok = row < __ldg(p.grp_tiles + 3 * mt + 2);
+      }
       mbar_wait(&tmem_full[acc], acc_phase);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
@@ -559,6 +572,29 @@ gemm_tc_cg2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+  gemm_tc_body<1, BN, false, false, EPI_F32, false, false, false, true>(tmA, tmB, tmA, tmB, tmA, p);
+}
+template <int BN>
+static cudaError_t launch_grouped(const CUtensorMap* maps, const TcParams& p, int max_tiles, int num_sms, cudaStream_t stream) {
+  using C = Cfg<1, BN, false>;
+  const int num_n = (p.N + BN - 1) / BN;
+  long units = static_cast<long>(max_tiles) * num_n;
+  if (units > num_sms) units = num_sms;
+  if (units < 1) units = 1;
+  auto kern = gemm_tc_grouped_kernel<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<static_cast<int>(units), kThreads, C::kTotal, stream>>>(maps[0], maps[1], p);
+  return cudaGetLastError();
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_batched_cg1_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                            const __grid_constant__ CUtensorMap tmD, const TcParams p) {
   gemm_tc_body<1, BN, false, false, EPI_BF16, false, true>(tmA, tmB, tmA, tmB, tmD, p);
@@ -717,6 +753,17 @@ extern "C" cudaError_t nrl_gemm_tc_batched(const CUtensorMap* maps, const nrl::t
   if (cg == 1 && bn == 256) return launch_batched<1, 256>(maps, *p, num_sms, stream);
   if (cg == 2 && bn == 128) return launch_batched<2, 128>(maps, *p, num_sms, stream);
   if (cg == 2 && bn == 256) return launch_batched<2, 256>(maps, *p, num_sms, stream);
+  return cudaErrorInvalidValue;
+}
+
+extern "C" cudaError_t nrl_gemm_tc_grouped(const CUtensorMap* maps, const nrl::tc::TcParams* p, int bn, int max_tiles, int num_sms,
+                                           cudaStream_t stream) {
+  using namespace nrl::tc;
+  if (p->grp_tiles == nullptr || p->grp_num_tiles == nullptr || p->out_f32 == nullptr || p->K2 != 0 || max_tiles < 1 || p->N % 4 != 0)
+    return cudaErrorInvalidValue;
+  if (bn == 64) return launch_grouped<64>(maps, *p, max_tiles, num_sms, stream);
+  if (bn == 128) return launch_grouped<128>(maps, *p, max_tiles, num_sms, stream);
+  if (bn == 256) return launch_grouped<256>(maps, *p, max_tiles, num_sms, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -33,6 +33,12 @@ struct TcParams {
   int* counters;                // [tiles] int32, zero between launches
   __nv_bfloat16* out_bf16;      // SPLIT: D written with plain stores (row stride out_stride elements)
   long out_stride;
+  // GROUPED kernels (mixture of experts): the rows of A are sorted by expert and B holds every expert's [N, K] matrix one after
+  // the other.  A row tile belongs to one expert; it may start at any row and is cut off at the end of the expert's rows
+  // (the tile's further rows are computed and dropped).  The table and its length live on the device (written by the
+  // routing kernels of the same stream), so no launch parameter depends on the routing.
+  const int* grp_tiles;         // [max tiles, 3]: expert, first row, end row (exclusive) of the expert's rows
+  const int* grp_num_tiles;     // [1]: row tiles in use
 };
 
 }  // namespace tc
@@ -44,6 +50,10 @@ extern "C" cudaError_t nrl_gemm_tc_fp8(const CUtensorMap* maps, const nrl::tc::T
                                        cudaStream_t stream);
 // batched K-major x K-major GEMM, bf16 out; maps = {A, B, D} 3D (tma_host.h make_tma_3d), B box rows = bn / cg
 extern "C" cudaError_t nrl_gemm_tc_batched(const CUtensorMap* maps, const nrl::tc::TcParams* p, int cg, int bn, int num_sms,
+                                           cudaStream_t stream);
+// grouped K-major x K-major GEMM with the float32 epilogue (cta_group 1); maps = {A [rows, K] box {128, 64}, B [experts * N, K]
+// box {bn, 64}}; out_f32 [rows, N]; p->N = columns per expert; max_tiles bounds the table's length (grid size)
+extern "C" cudaError_t nrl_gemm_tc_grouped(const CUtensorMap* maps, const nrl::tc::TcParams* p, int bn, int max_tiles, int num_sms,
                                            cudaStream_t stream);
 extern "C" cudaError_t nrl_gemm_tc(const CUtensorMap* maps, const nrl::tc::TcParams* p, int cg, int bn, int a_mn, int b_mn,
                                    int epi, int num_sms, cudaStream_t stream);

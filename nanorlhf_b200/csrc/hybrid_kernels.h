@@ -48,6 +48,20 @@ cudaError_t nrl_group_norm_residual(float* x, const float* o, const float* gate,
 cudaError_t nrl_moe_route(const float* router, long sr, const float* router_bias, int E, int top, const float* gu, long sgu, int ff,
                           void* act, long sa, int act_f32, int* ids, float* wts, int T, cudaStream_t s);
 
+// Grouped (sorted by expert) form of a mixture of experts, moe.cu.  ids int [R = T * top] from nrl_moe_route.
+//   nrl_moe_plan: slot_of[R] = row of every (token, choice) pair in expert order, row_token[R] = token of every row,
+//     seg[E + 1] = first row of every expert, tiles [*, 3] = (expert, first row, end row of the expert) per `tile_rows` rows of
+//     an expert (at most ceil(R / tile_rows) + E of them), num_tiles[1]: the table of the grouped GEMM (gemm_tc.h).
+//   nrl_gather_rows16: out[r] = in[row_token[r]] for rows of W 16-bit elements.
+//   nrl_swiglu_rows: act[r, c] (bf16) = silu(gu[r, c]) * gu[r, ff + c].
+//   nrl_moe_combine: out[t] (float) = sum_k wts[t, k] * y[slot_of[t * top + k]] in the order of k.
+cudaError_t nrl_moe_plan(const int* ids, int R, int top, int E, int tile_rows, int* slot_of, int* row_token, int* seg, int* tiles,
+                         int* num_tiles, cudaStream_t s);
+cudaError_t nrl_gather_rows16(const void* in, long in_stride, const int* row_token, void* out, int R, int W, cudaStream_t s);
+cudaError_t nrl_swiglu_rows(const float* gu, long sg, void* act, long sa, int R, int ff, cudaStream_t s);
+cudaError_t nrl_moe_combine(const float* y, long sy, const int* slot_of, const float* wts, int top, float* out, long so, int T, int W,
+                            cudaStream_t s);
+
 // Layer boundary of a depth-weighted residual stream.  results: float [n_results_cap, stride_r] with rows of W.
 //   if (o)  results[i] = xprev + o                      (closes the previous layer)
 //   x = sum_{j <= i} dw[j] * results[j]   (dw == nullptr: x = results[i])      -> xcur (float)
@@ -132,9 +146,9 @@ int nrl_window_attention_splits(int T, int Hq, int Hkv, int window, int max_bloc
 cudaError_t nrl_window_attention_decode(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                         int max_blocks, const int* tok_entry, const int* pos, int window, float scale,
                                         float out_scale, void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page,
-                                        int nsplit, float* part, cudaStream_t s);
+                                        int nsplit, float* part, const NrlAttnMods* mods, cudaStream_t s);
 cudaError_t nrl_window_attention_mma(const float* q, long sq, const void* k_cache, const void* v_cache, const int* block_table,
                                      int max_blocks, const int* tok_entry, const int* pos, int window, float scale, float out_scale,
                                      void* out, long so, int T, int Hq, int Hkv, int D, int Dv, int page, int single_token,
-                                     cudaStream_t s);
+                                     const NrlAttnMods* mods, cudaStream_t s);
 }

@@ -142,7 +142,9 @@ class VilosunConfig:
             if m.kind == "conv_attention":
                 for n, rows in (("q", m.heads * m.dim), ("k", m.kv_heads * m.dim), ("v", m.kv_heads * m.vdim)):
                     out.update({q + n: (rows, W), q + n + ".b": (rows,), q + n + ".conv": (rows, m.conv)})
-                out.update({q + "vmix": (), q + "temp": (m.heads,), q + "g": (m.heads, W), q + "o": (W, m.heads * m.vdim)})
+                if m.v_blend >= 0 and m.v_blend != spec.index:        # the blend weight exists only where values are blended
+                    out[q + "vmix"] = ()
+                out.update({q + "temp": (m.heads,), q + "g": (m.heads, W), q + "o": (W, m.heads * m.vdim)})
             else:
                 nk, nv = m.kv_heads * m.dim, m.heads * m.vdim
                 out.update({q + "q": (nk, W), q + "q.conv": (nk, m.conv), q + "k": (nk, W), q + "k.conv": (nk, m.conv),

@@ -107,3 +107,25 @@ def moe_route(router, router_bias, top, gu=None, ff=0, act=None, ids=None, wts=N
     """Top-k routing (softmax over the chosen logits); with ``gu`` / ``act`` also the dense-form expert activations."""
     native._count()
     _ext().moe_route(router, router_bias, top, gu, ff, act, ids, wts)
+
+
+def moe_grouped_ffn(h, ids, wts, w_gate_up, w_down, experts, ff, out):
+    """Expert feed-forwards of a routed batch on the grouped tcgen05 GEMM.  ``h`` bf16 [T, W]; ``ids`` / ``wts`` [T, top] from
+    ``moe_route``; ``w_gate_up`` bf16 [experts * 2 ff, W] (per expert its gate rows, then its up rows); ``w_down`` bf16
+    [experts * W, ff]; ``out`` float [T, W] = sum_k wts[t, k] * expert_k(h[t]).  Six launches, none depends on the routing."""
+    import torch
+    T, W = h.shape
+    R = ids.numel()
+    ext = _ext()
+    native._count(6)
+    slot_of, row_token, _seg, tiles, num_tiles = ext.moe_plan(ids, experts, 128)
+    xp = torch.empty(R, W, dtype=h.dtype, device=h.device)
+    ext.gather_rows(h, row_token, xp)
+    gu = torch.empty(R, 2 * ff, dtype=torch.float32, device=h.device)
+    ext.gemm_tc_grouped(xp, w_gate_up, gu, tiles, num_tiles)
+    act = torch.empty(R, ff, dtype=h.dtype, device=h.device)
+    ext.swiglu_rows(gu, act)
+    y = torch.empty(R, W, dtype=torch.float32, device=h.device)
+    ext.gemm_tc_grouped(act, w_down, y, tiles, num_tiles)
+    ext.moe_combine(y, slot_of, wts, out)
+    return out

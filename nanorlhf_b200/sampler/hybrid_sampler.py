@@ -60,7 +60,7 @@ class _Layer:
     """One pair of fused matrices with what runs between them: a whole layer of a depth-weighted stream (mixers and the
     feed-forward side by side), or one sublayer of a sandwich stream (the mixer, or the feed-forward)."""
     __slots__ = ("spec", "gain", "dw", "w_in", "w_out", "mixers", "ff_col", "ff_out_col", "n_in", "k_out", "out_pad",
-                 "w_pre", "w_post", "gate_col", "gate_bias", "router_col", "router_bias")
+                 "w_pre", "w_post", "gate_col", "gate_bias", "router_col", "router_bias", "w_gate_up", "w_down")
 
 
 def _pad8(n: int) -> int:
@@ -72,7 +72,7 @@ class HybridSampler:
 
     def __init__(self, model, dtype: str = "bf16", kv_block_size: int = 16, max_num_seqs: int = 64, pool_tokens: Optional[int] = None,
                  prefill_token_budget: int = 8192, gemm: str = "tc", rollout_dtype: Optional[str] = None,
-                 use_cuda_graph: bool = True, **_unused):
+                 use_cuda_graph: bool = True, moe: str = "auto", **_unused):
         if kv_block_size != self.PAGE:
             raise ValueError("KV pages hold 16 tokens")
         native.load()
@@ -92,6 +92,9 @@ class HybridSampler:
             torch.backends.cuda.matmul.allow_tf32 = False
             torch.backends.cudnn.allow_tf32 = False
         self.gemm_backend = gemm
+        if moe not in ("auto", "grouped", "dense"):
+            raise ValueError(f"unknown mixture-of-experts form {moe!r}")
+        self.moe_form = moe                                # "auto": grouped tcgen05 GEMM in bf16 when the sizes fit, else dense
         self.max_num_seqs = max_num_seqs
         self.pool_tokens = pool_tokens
         self.prefill_token_budget = prefill_token_budget
@@ -157,6 +160,7 @@ class HybridSampler:
         L = _Layer()
         L.spec = spec
         L.gain = L.dw = L.w_pre = L.w_post = L.gate_col = L.gate_bias = L.router_col = L.router_bias = None
+        L.w_gate_up = L.w_down = None
         rows_in: List[torch.Tensor] = []
         cols_out: List[torch.Tensor] = []
         n_in = k_out = 0
@@ -232,7 +236,15 @@ class HybridSampler:
             if spec.ff_kind == "dense":
                 L.ff_col = add_in(p + "mlp.up")
                 L.ff_out_col = add_out(p + "mlp.down")
-            elif spec.ff_kind == "moe":                   # router, then per expert its gate rows and its up rows
+            elif spec.ff_kind == "moe" and self._moe_grouped(spec):
+                # sorted-by-expert form: only the router rides in the fused matrix; the experts' matrices are stacked for the
+                # grouped GEMM, [experts * 2 ff, W] (gate rows, then up rows) and [experts * W, ff]
+                L.router_col = add_in(p + "mlp.router")
+                L.router_bias = self._f(p + "mlp.router.b") if self.lm.has_tensor(p + "mlp.router.b") else None
+                L.w_gate_up = torch.cat([self._t(f"{p}mlp.e{e}.{n}").to(device=dev, dtype=wd) for e in range(spec.experts)
+                                         for n in ("gate", "up")], 0).contiguous()
+                L.w_down = torch.cat([self._t(f"{p}mlp.e{e}.down").to(device=dev, dtype=wd) for e in range(spec.experts)], 0).contiguous()
+            elif spec.ff_kind == "moe":                   # dense form: router, then per expert its gate rows and its up rows
                 L.router_col = add_in(p + "mlp.router")
                 L.router_bias = self._f(p + "mlp.router.b") if self.lm.has_tensor(p + "mlp.router.b") else None
                 c0 = n_in
@@ -254,8 +266,15 @@ class HybridSampler:
         L.w_in = torch.zeros(L.n_in, W, dtype=wd, device=dev)
         L.w_in[:n_in] = torch.cat([t.to(device=dev, dtype=wd) for t in rows_in], 0)
         L.w_out = torch.zeros(W, L.k_out, dtype=wd, device=dev)
-        L.w_out[:, :k_out] = torch.cat([t.to(device=dev, dtype=wd) for t in cols_out], 1)
+        if cols_out:
+            L.w_out[:, :k_out] = torch.cat([t.to(device=dev, dtype=wd) for t in cols_out], 1)
         return L
+
+    def _moe_grouped(self, spec) -> bool:
+        fits = not self.fp32 and self.cfg.width % 8 == 0 and spec.ff % 8 == 0
+        if self.moe_form == "grouped" and not fits:
+            raise ValueError("the grouped mixture-of-experts form needs bf16 serving and width / expert width that are multiples of 8")
+        return fits and self.moe_form != "dense"
 
     def weights_fingerprint(self):
         return getattr(self.lm, "_nrl_version", 0)
@@ -410,7 +429,9 @@ class HybridSampler:
                     self._ssd(M, U, plan, eps, out)
             if L.ff_col is not None:
                 self._feed_forward(L, U, A)
-            o = self._mm(A, L.w_out)                                                  # [T, W] float
+            o = self._mm(A, L.w_out) if L.k_out else None                             # [T, W] float
+            if L.w_gate_up is not None:
+                o = self._experts_grouped(L, U, h, o)
             gate = None
             if L.gate_col is not None:
                 c, n = L.gate_col
@@ -423,11 +444,26 @@ class HybridSampler:
         if not rows:
             return torch.empty(0, cfg.vocab, **f32)
         hw = h if rows == list(range(T)) else h[torch.tensor(rows, device=dev)]
-        logits = self._mm(hw.contiguous(), self.head)[:, :cfg.vocab]
+        logits = self._mm(hw.contiguous(), self.head)
         if st.logit_scale != 1.0:
             native._count()
-            logits = logits * st.logit_scale
-        return logits
+            logits.mul_(st.logit_scale)
+        return logits[:, :cfg.vocab]                      # rows keep their padded (16-byte aligned) stride
+
+    def _experts_grouped(self, L, U, h, o):
+        """Route, then run only the chosen experts: rows sorted by expert through two grouped GEMMs."""
+        spec = L.spec
+        T, dev = h.shape[0], h.device
+        rc, E = L.router_col
+        ids = torch.empty(T, spec.top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, spec.top, dtype=torch.float32, device=dev)
+        hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, ids=ids, wts=wts)
+        y = torch.empty(T, self.cfg.width, dtype=torch.float32, device=dev)
+        hy.moe_grouped_ffn(h, ids, wts, L.w_gate_up, L.w_down, E, spec.ff, y)
+        if o is None:
+            return y
+        native._count()
+        return o.add_(y)
 
     def _feed_forward(self, L, U, A):
         spec = L.spec
@@ -488,6 +524,8 @@ class HybridSampler:
             if L.ff_col is not None:
                 self._feed_forward(L, U, A)
             o = self._mm(A, L.w_out)                                                  # [T, W] float
+            if L.w_gate_up is not None:
+                o = self._experts_grouped(L, U, h, o)
             xprev = xcur
         hy.stream_norm(results, nl, o, xprev, self.layers[-1].dw, self.final_gain, eps, xbuf[nl & 1], h, T)
         if not rows:

@@ -60,9 +60,34 @@ def causal_conv(u, w):
     return y
 
 
+def distance_slopes(H):
+    """Head h of H (from 0) loses 2^(-8 (h + 1) / H) of score per position between query and key."""
+    return [2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]
+
+
+def chunk_softmax_attention(q, k, v, size, scale, temp=None, slopes=None):
+    """Core of the attention mixer on given q [T, H, D], k [T, G, D], v [T, G, Dv]: position i attends to j <= i with
+    floor(i / size) == floor(j / size); score = q.k * scale * temp[h] - slopes[h] * (i - j); ordinary softmax."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
+    for i in range(T):
+        lo = (i // size) * size
+        dist = torch.arange(i - lo, -1, -1, dtype=F64)       # i - j for j = lo .. i
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (k[lo:i + 1, g] @ q[i, hh]) * scale
+            if temp is not None:
+                s = s * temp[hh]
+            if slopes is not None:
+                s = s - slopes[hh] * dist
+            out[i, hh] = torch.softmax(s, 0) @ v[lo:i + 1, g]
+    return out
+
+
 def chunk_attention(h, W, p, m, v_first=None):
-    """Softmax attention inside fixed chunks of positions, with a linear distance penalty, a learned temperature per head and a
-    sigmoid gate per head.  Returns (mixer output, the values that were attended = what a cache would hold)."""
+    """The attention mixer: biased projections, short convolutions, value blending, chunked attention, a sigmoid gate per head.
+    Returns (mixer output, the values that were attended = what a cache would hold)."""
     T = h.shape[0]
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = causal_conv(lin(W[p + "q"], h, W[p + "q.b"]), W[p + "q.conv"]).view(T, H, D)
@@ -71,18 +96,8 @@ def chunk_attention(h, W, p, m, v_first=None):
     if v_first is not None:
         lam = W[p + "vmix"].to(F64)
         v = (1 - lam) * v + lam * v_first
-    size = m["mask"]["size"]
-    temp = W[p + "temp"].to(F64)
-    gate = torch.sigmoid(lin(W[p + "g"], h))                 # [T, H]
-    out = torch.zeros(T, H, Dv, dtype=F64)
-    for i in range(T):
-        lo = (i // size) * size
-        dist = torch.arange(i - lo, -1, -1, dtype=F64)       # i - j for j = lo .. i
-        for hh in range(H):
-            g = hh // (H // G)
-            slope = 2.0 ** (-8.0 * (hh + 1) / H)
-            s = (k[lo:i + 1, g] @ q[i, hh]) * m["scale"] * temp[hh] - slope * dist
-            out[i, hh] = (torch.softmax(s, 0) @ v[lo:i + 1, g]) * gate[i, hh]
+    out = chunk_softmax_attention(q, k, v, m["mask"]["size"], m["scale"], W[p + "temp"].to(F64), distance_slopes(H))
+    out = out * torch.sigmoid(lin(W[p + "g"], h)).unsqueeze(-1)
     return lin(W[p + "o"], out.reshape(T, H * Dv)), v
 
 
@@ -126,7 +141,7 @@ def moe(h, W, p, mlp):
     return out
 
 
-def forward(tokens, W, cfg, return_layers=False):
+def forward(cfg, W, tokens, return_layers=False):
     """Logits [T, vocab] of one whole sequence (and the stream after every layer)."""
     eps, groups = cfg["norm"]["eps"], cfg["norm"]["groups"]
     x = embed(list(tokens), W, cfg)
@@ -214,3 +229,33 @@ def random_weights(cfg, seed=0, dtype=torch.bfloat16):
     W["final.norm"] = gain(width)
     W["head"] = rn(cfg["vocab"], width, s=width ** -0.5)
     return {k: v.to(dtype) for k, v in W.items()}
+
+
+def make_config(vocab=97, width=48, layers=("attention", "delta"), groups=2, eps=1e-5, embed_scale=3.0, logit_scale=0.5,
+                bigram=(61, 7, 13), attn=None, delta=None, moe=None, v_mix=None, chunk=None):
+    """A small config dict.  ``attn`` / ``delta`` / ``moe`` override sizes; ``v_mix`` / ``chunk``: per attention layer (in order)
+    lists overriding the flag / the chunk length; ``moe=None`` in a position of ``layers`` spelled "attention-" or "delta-"
+    drops that layer's feed-forward."""
+    a = dict(heads=4, kv_heads=2, dim=8, vdim=12, conv=3, size=6, scale=0.4)
+    a.update(attn or {})
+    d = dict(heads=4, kv_heads=2, dim=12, vdim=8, conv=2)
+    d.update(delta or {})
+    f = dict(ff=16, experts=5, top=2)
+    f.update(moe or {})
+    out, na = [], 0
+    for kind in layers:
+        bare = kind.endswith("-")
+        kind = kind.rstrip("-")
+        mlp = None if bare else {"kind": "moe", "expert": {"ff": f["ff"]}, "router": {"experts": f["experts"], "top": f["top"]}}
+        if kind == "attention":
+            m = {"heads": a["heads"], "kv_heads": a["kv_heads"], "dim": a["dim"], "vdim": a["vdim"], "conv": a["conv"],
+                 "scale": a["scale"], "mask": {"size": chunk[na] if chunk else a["size"]}, "v_mix": v_mix[na] if v_mix else True}
+            na += 1
+        else:
+            m = {"heads": d["heads"], "kv_heads": d["kv_heads"], "dim": d["dim"], "vdim": d["vdim"], "conv": d["conv"]}
+        out.append({"type": kind, "mixer": m, "mlp": mlp})
+    emb = {"scale": embed_scale}
+    if bigram:
+        emb["bigram"] = {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}
+    return {"architecture": "Vilosun", "vocab": vocab, "width": width, "norm": {"eps": eps, "groups": groups}, "embedding": emb,
+            "logit_scale": logit_scale, "layers": out}
