@@ -205,6 +205,31 @@ def kernels_vilosun(width=2048, batch=16, prompt_len=2048, chunk=1024, decode_ba
         ub = torch.empty(T, 4 * width, dtype=torch.bfloat16, device=dev)
         sec = _time(lambda: hy.act_cols(up, ub, "relu2"))
         report(f"{phase}.nezavik.relu2", sec, T * 4 * width * 6.0)
+        del U, A, up, ub
+        # -- the experts on the grouped GEMM (routing plan, gather, two grouped GEMMs, SwiGLU, combine) vs the dense pair of GEMMs
+        #    of a feed-forward with as many active weights (4 x width, squared ReLU)
+        from nanorlhf_b200.ops import gemm as _gemm
+        hb_ = torch.randn(T, width, device=dev).bfloat16()
+        zr = torch.randn(T, experts, **f32)
+        ids, wts = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, **f32)
+        hy.moe_route(zr, None, top, ids=ids, wts=wts)
+        wgu = (torch.randn(experts * 2 * ff, width, device=dev) * width ** -0.5).bfloat16()
+        wdn = (torch.randn(experts * width, ff, device=dev) * ff ** -0.5).bfloat16()
+        yo = torch.empty(T, width, **f32)
+        sec = _time(lambda: hy.moe_grouped_ffn(hb_, ids, wts, wgu, wdn, experts, ff, yo), iters=5, warm=2)
+        active = min(experts, T * top)                     # experts whose weights a step has to read
+        wbytes = active * 3.0 * ff * width * 2.0
+        report(f"{phase}.moe_grouped_ffn({experts} experts top {top}, ff {ff})", sec, wbytes + T * width * 6.0, flops=6.0 * T * top * width * ff)
+        w1 = (torch.randn(4 * width, width, device=dev) * width ** -0.5).bfloat16()
+        w2 = (torch.randn(width, 4 * width, device=dev) * (4 * width) ** -0.5).bfloat16()
+        u1, a1, o1 = torch.empty(T, 4 * width, **f32), torch.empty(T, 4 * width, dtype=torch.bfloat16, device=dev), torch.empty(T, width, **f32)
+
+        def dense_ffn():
+            _gemm.gemm(hb_, w1, out_f32=u1)
+            hy.act_cols(u1, a1, "relu2")
+            _gemm.gemm(a1, w2, out_f32=o1)
+        sec = _time(dense_ffn, iters=5, warm=2)
+        report(f"{phase}.nezavik.dense_ffn(4 x width)", sec, 8.0 * width * width * 2.0 + T * width * 6.0, flops=16.0 * T * width * width)
     return out
 
 

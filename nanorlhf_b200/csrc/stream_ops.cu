@@ -191,6 +191,86 @@ __global__ void group_norm_residual_kernel(float* __restrict__ x, const float* _
   }
 }
 
+// The same boundary with 128-bit accesses and the group's values held in registers between the passes (NV float4 per thread):
+// o, the gate and x are read once, x and h written once.  Needs W / groups % 4 == 0 and 16-byte aligned rows.
+template <typename HT, int NV>
+__global__ void group_norm_residual_vec_kernel(float* __restrict__ x, const float* __restrict__ o, const float* __restrict__ gate,
+                                               long sg, const float* __restrict__ gate_bias, const float* __restrict__ w_post,
+                                               const float* __restrict__ w_pre, int groups, float eps, HT* __restrict__ h, int W) {
+  __shared__ float red[32];
+  const long row = static_cast<long>(blockIdx.x) * W;
+  const int part = W / groups, part4 = part >> 2;
+  const float inv = 1.f / static_cast<float>(part);
+  for (int g = 0; g < groups; ++g) {
+    const int c0 = g * part;
+    float v[NV][4];
+    if (o != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i4 = threadIdx.x + k * blockDim.x;
+        v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0.f;
+        if (i4 < part4) {
+          const int c = c0 + i4 * 4;
+          ldv<4>(o + row + c, v[k]);
+          if (gate != nullptr) {
+            float gv[4], gb[4] = {0.f, 0.f, 0.f, 0.f};
+            ldv<4>(gate + blockIdx.x * sg + c, gv);
+            if (gate_bias != nullptr) ldv<4>(gate_bias + c, gb);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[k][e] *= sigmoidf_(gv[e] + gb[e]);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ss += v[k][e] * v[k][e];
+        }
+      }
+      ss = block_sum(ss, red);
+      const float r = 1.f / sqrtf(ss * inv + eps);
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i4 = threadIdx.x + k * blockDim.x;
+        if (i4 < part4) {
+          const int c = c0 + i4 * 4;
+          float xv[4], wv[4];
+          ldv<4>(x + row + c, xv);
+          ldv<4>(w_post + c, wv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[k][e] = xv[e] + v[k][e] * r * wv[e];
+          st4(x + row + c, v[k]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i4 = threadIdx.x + k * blockDim.x;
+        v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0.f;
+        if (i4 < part4) ldv<4>(x + row + c0 + i4 * 4, v[k]);
+      }
+    }
+    if (h != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += v[k][e] * v[k][e];
+      ss = block_sum(ss, red);
+      const float r = 1.f / sqrtf(ss * inv + eps);
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i4 = threadIdx.x + k * blockDim.x;
+        if (i4 < part4) {
+          const int c = c0 + i4 * 4;
+          float wv[4], hv[4];
+          ldv<4>(w_pre + c, wv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) hv[e] = v[k][e] * r * wv[e];
+          st4(h + row + c, hv);
+        }
+      }
+    }
+  }
+}
+
 // Mixture-of-experts routing and (dense form) expert activations, one block per token.
 //   z = router[t, :E] + router_bias;  the `top` largest (ties: lowest index) get softmax(z over the chosen) as weights
 //   ids [T, top] int, wts [T, top] float (if not null)
@@ -395,6 +475,7 @@ cudaError_t launch_gated_norm(const float* y, long sy, const float* gate, long s
 }
 }  // namespace
 
+
 namespace {
 inline bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
 }  // namespace
@@ -436,6 +517,28 @@ cudaError_t nrl_group_norm_residual(float* x, const float* o, const float* gate,
   if (T <= 0) return cudaSuccess;
   if (groups < 1 || W % groups != 0 || (o != nullptr && w_post == nullptr) || (h != nullptr && w_pre == nullptr)) return cudaErrorInvalidValue;
   const int part = W / groups;
+  const bool vec = part % 4 == 0 && sg % 4 == 0 && aligned(x, 16) && (o == nullptr || aligned(o, 16)) && (gate == nullptr || aligned(gate, 16)) &&
+                   (gate_bias == nullptr || aligned(gate_bias, 16)) && (w_post == nullptr || aligned(w_post, 16)) &&
+                   (w_pre == nullptr || aligned(w_pre, 16)) && (h == nullptr || aligned(h, h_f32 ? 16 : 8)) && part <= 8 * 4 * 256;
+  if (vec) {
+    const int part4 = part / 4;
+    int tv = part4 <= 32 ? 32 : part4 <= 64 ? 64 : part4 <= 256 ? 128 : 256;      // up to 2 float4 per thread before the block grows
+    const int nv = (part4 + tv - 1) / tv;
+#define NRL_GNR(HT_, NV_)                                                                                                          \
+  group_norm_residual_vec_kernel<HT_, NV_><<<T, tv, 0, s>>>(x, o, gate, sg, gate_bias, w_post, w_pre, groups, eps, static_cast<HT_*>(h), W)
+#define NRL_GNR_NV(HT_)                                                                                                            \
+  do {                                                                                                                             \
+    if (nv <= 1) NRL_GNR(HT_, 1);                                                                                                  \
+    else if (nv <= 2) NRL_GNR(HT_, 2);                                                                                             \
+    else if (nv <= 4) NRL_GNR(HT_, 4);                                                                                             \
+    else NRL_GNR(HT_, 8);                                                                                                          \
+  } while (0)
+    if (h_f32) NRL_GNR_NV(float);
+    else NRL_GNR_NV(__nv_bfloat16);
+#undef NRL_GNR_NV
+#undef NRL_GNR
+    return cudaGetLastError();
+  }
   const int th = part >= 1024 ? 256 : part >= 128 ? 128 : 64;
   if (h_f32)
     group_norm_residual_kernel<float><<<T, th, 0, s>>>(x, o, gate, sg, gate_bias, w_post, w_pre, groups, eps, static_cast<float*>(h), W);
