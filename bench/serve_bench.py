@@ -74,7 +74,7 @@ def vilosun_config(width: int, n_layers: int, vocab: int, chunk: int = 1024, exp
     dl = {"type": "delta", "mlp": mlp, "mixer": {"conv": 4, "dim": 128, "vdim": 128, "heads": H, "kv_heads": H}}
     pattern = [at, dl, dl, at]
     return VilosunConfig.from_dict({"architecture": "Vilosun", "layers": [pattern[i % 4] for i in range(n_layers)],
-                                    "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+                                    "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 48271, "mul_cur": 16807}},
                                     "logit_scale": 1.0, "norm": {"eps": 1e-6, "groups": 2}, "vocab": vocab, "width": width})
 
 
@@ -151,7 +151,7 @@ def kernels_vilosun(width=2048, batch=16, prompt_len=2048, chunk=1024, decode_ba
         # -- embeddings
         emb, pair = torch.randn(32768, width, device=dev).bfloat16(), torch.randn(65522, width, device=dev).bfloat16()
         prev, x0 = torch.zeros(B, dtype=torch.int32, device=dev), torch.empty(T, width, **f32)
-        sec = _time(lambda: hy.embed_hashed(emb, pair, plan, prev, 1.0, 31, 17, 65521, x0))
+        sec = _time(lambda: hy.embed_hashed(emb, pair, plan, prev, 1.0, 48271, 16807, 65521, x0))
         report(f"{phase}.embed_hashed", sec, T * width * 8.0)
         pos_t = torch.randn(8192, width, device=dev).bfloat16()
         sec = _time(lambda: hy.embed_pos(emb, pos_t, plan.tokens, plan.pos, x0))
@@ -201,6 +201,9 @@ def kernels_vilosun(width=2048, batch=16, prompt_len=2048, chunk=1024, decode_ba
         rb = torch.zeros(experts, **f32)
         sec = _time(lambda: hy.moe_route(U[:, :experts], rb, top, gu=U[:, experts:], ff=ff, act=A))
         report(f"{phase}.moe_route(dense form, {experts} experts top {top})", sec, T * (experts * 4.0 + top * ff * 8.0 + experts * ff * 2.0))
+        ids_, wts_ = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, **f32)
+        sec = _time(lambda: hy.moe_route(U[:, :experts], rb, top, ids=ids_, wts=wts_))
+        report(f"{phase}.moe_route(ids and weights only)", sec, T * (experts * 4.0 + top * 8.0))
         up = torch.randn(T, 4 * width, **f32)
         ub = torch.empty(T, 4 * width, dtype=torch.bfloat16, device=dev)
         sec = _time(lambda: hy.act_cols(up, ub, "relu2"))
@@ -216,7 +219,7 @@ def kernels_vilosun(width=2048, batch=16, prompt_len=2048, chunk=1024, decode_ba
         wgu = (torch.randn(experts * 2 * ff, width, device=dev) * width ** -0.5).bfloat16()
         wdn = (torch.randn(experts * width, ff, device=dev) * ff ** -0.5).bfloat16()
         yo = torch.empty(T, width, **f32)
-        sec = _time(lambda: hy.moe_grouped_ffn(hb_, ids, wts, wgu, wdn, experts, ff, yo), iters=5, warm=2)
+        sec = _time(lambda: hy.moe_grouped_ffn(hb_, ids, wts, wgu, wdn, experts, ff, yo, fused_act=ff % 32 == 0), iters=5, warm=2)
         active = min(experts, T * top)                     # experts whose weights a step has to read
         wbytes = active * 3.0 * ff * width * 2.0
         report(f"{phase}.moe_grouped_ffn({experts} experts top {top}, ff {ff})", sec, wbytes + T * width * 6.0, flops=6.0 * T * top * width * ff)

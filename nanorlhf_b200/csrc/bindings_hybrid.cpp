@@ -333,31 +333,43 @@ void moe_combine(const Tensor& y, const Tensor& slot_of, const Tensor& wts, Tens
         "moe_combine");
 }
 
-// out[r, :] = a[r, :] . b[expert(r)]^T for rows sorted by expert: a bf16 [R, K], b bf16 [E * N, K], out float [R, N];
-// tiles / num_tiles from moe_plan (128-row tiles).
-void gemm_tc_grouped(const Tensor& a, const Tensor& b, Tensor out, const Tensor& tiles, const Tensor& num_tiles, int64_t block_n) {
+// Rows sorted by expert: a bf16 [R, K], b bf16 [E * N, K]; tiles / num_tiles from moe_plan (128-row tiles).
+//   out float [R, N] = a[r] . b[expert(r)]^T,  or
+//   act bf16 [R, N / 2] = silu(gate) * up with b's rows interleaved per 32 features ([32 gate rows | 32 up rows], N % 64 == 0).
+void gemm_tc_grouped(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& out, const Tensor& tiles, const Tensor& num_tiles,
+                     int64_t block_n, const c10::optional<Tensor>& act) {
   c10::cuda::CUDAGuard guard(a.device());
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && a.dim() == 2 &&
                   b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_tc_grouped: bf16 2D operands with unit inner stride");
   TORCH_CHECK((a.stride(0) * 2) % 16 == 0 && (b.stride(0) * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "gemm_tc_grouped: 16-byte aligned rows");
-  const int64_t R = a.size(0), K = a.size(1), N = out.size(1);
+  TORCH_CHECK(out.has_value() != act.has_value(), "gemm_tc_grouped: give either the float result or the activation output");
+  const int64_t R = a.size(0), K = a.size(1), N = out.has_value() ? out->size(1) : 2 * act->size(1);
   TORCH_CHECK(b.size(1) == K && K % 8 == 0 && N % 8 == 0 && b.size(0) % N == 0, "gemm_tc_grouped: b [E * N, K], K and N multiples of 8");
-  TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.dim() == 2 && out.size(0) == R && out.stride(1) == 1 && out.stride(0) % 4 == 0 &&
-                  (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "gemm_tc_grouped: out float [R, N], 16-byte aligned rows");
   TORCH_CHECK(tiles.scalar_type() == torch::kInt32 && tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 3 &&
                   num_tiles.scalar_type() == torch::kInt32 && num_tiles.numel() == 1, "gemm_tc_grouped: tile table");
+  nrl::tc::TcParams p{};
+  if (out.has_value()) {
+    TORCH_CHECK(out->scalar_type() == torch::kFloat32 && out->dim() == 2 && out->size(0) == R && out->stride(1) == 1 &&
+                    out->stride(0) % 4 == 0 && (reinterpret_cast<uintptr_t>(out->data_ptr()) & 15) == 0,
+                "gemm_tc_grouped: out float [R, N], 16-byte aligned rows");
+    p.out_f32 = out->data_ptr<float>();
+    p.out_f32_stride = out->stride(0);
+  } else {
+    TORCH_CHECK(act->scalar_type() == torch::kBFloat16 && act->dim() == 2 && act->size(0) == R && act->stride(1) == 1 &&
+                    act->stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(act->data_ptr()) & 15) == 0 && N % 64 == 0,
+                "gemm_tc_grouped: act bf16 [R, N / 2], 16-byte aligned rows, N a multiple of 64");
+    p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(act->data_ptr());
+    p.out_stride = act->stride(0);
+  }
   if (R == 0) return;
   const int bn = block_n > 0 ? static_cast<int>(block_n) : (N <= 64 ? 64 : 128);
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap maps[2];
   maps[0] = nrl::make_tma_2d(a.data_ptr(), a.size(0), a.size(1), a.stride(0) * 2, 128, 64, BF, 2);
   maps[1] = nrl::make_tma_2d(b.data_ptr(), b.size(0), b.size(1), b.stride(0) * 2, bn, 64, BF, 2);
-  nrl::tc::TcParams p{};
   p.M = static_cast<int>(R); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.K2 = 0;
   p.alpha = 1.f;
-  p.out_f32 = out.data_ptr<float>();
-  p.out_f32_stride = out.stride(0);
   p.grp_tiles = tiles.data_ptr<int>();
   p.grp_num_tiles = num_tiles.data_ptr<int>();
   int sms = 0, dev = 0;
@@ -374,8 +386,9 @@ void bind_hybrid(pybind11::module_& m) {
   m.def("gather_rows", &gather_rows, "out[r] = in[row_token[r]] (bf16 rows)");
   m.def("swiglu_rows", &swiglu_rows, "act = silu(gu[:, :ff]) * gu[:, ff:] (float in, bf16 out)");
   m.def("moe_combine", &moe_combine, "out[t] = sum_k wts[t, k] y[slot_of[t, k]]");
-  m.def("gemm_tc_grouped", &gemm_tc_grouped, "grouped tcgen05 GEMM over rows sorted by expert, float32 out", pybind11::arg("a"),
-        pybind11::arg("b"), pybind11::arg("out"), pybind11::arg("tiles"), pybind11::arg("num_tiles"), pybind11::arg("block_n") = 0);
+  m.def("gemm_tc_grouped", &gemm_tc_grouped, "grouped tcgen05 GEMM over rows sorted by expert: float32 out, or fused SwiGLU bf16 out",
+        pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("out"), pybind11::arg("tiles"), pybind11::arg("num_tiles"),
+        pybind11::arg("block_n") = 0, pybind11::arg("act") = pybind11::none());
   m.def("embed_pos", &embed_pos, "x0 = embed[tok] + pos_table[pos] (float)");
   m.def("stream_norm", &stream_norm, "close a layer, form the depth-weighted stream and its single-gain RMS norm");
   m.def("act_cols", &act_cols, "typed out = act(float in): 0 copy, 1 relu^2");

@@ -443,7 +443,25 @@ NRL_DEVICE void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB, con
           }
         }
         const int col0 = c.n_blk * BN + ch * 64;
-        if (EPI == EPI_F32) {
+        if (EPI == EPI_F32 && GROUPED && p.out_bf16 != nullptr) {
+          // grouped gate / up projection with the SwiGLU formed here: B rows are interleaved per 32 features ([32 gate | 32 up]
+          // in every 64-column chunk), so a chunk yields 32 activations of this row: 64 contiguous bytes, plain masked stores
+          const int f0 = c.n_blk * (BN / 2) + ch * 32;
+          if (row_ok && f0 < p.N / 2) {
+            __nv_bfloat16* orow = p.out_bf16 + static_cast<long>(row) * p.out_stride + f0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float g0 = __uint_as_float(v[0][j + 2 * e]), g1 = __uint_as_float(v[0][j + 2 * e + 1]);
+                const float u0 = __uint_as_float(v[1][j + 2 * e]), u1 = __uint_as_float(v[1][j + 2 * e + 1]);
+                pk[e] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              }
+              *reinterpret_cast<uint4*>(orow + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
+        } else if (EPI == EPI_F32) {
           // fp32 row-major out (+)= alpha * acc : thread = row, 2 x 128 contiguous bytes per chunk
           if (row_ok) {
             float* orow = p.out_f32 + static_cast<long>(row) * p.out_f32_stride + col0;
@@ -759,8 +777,8 @@ extern "C" cudaError_t nrl_gemm_tc_batched(const CUtensorMap* maps, const nrl::t
 extern "C" cudaError_t nrl_gemm_tc_grouped(const CUtensorMap* maps, const nrl::tc::TcParams* p, int bn, int max_tiles, int num_sms,
                                            cudaStream_t stream) {
   using namespace nrl::tc;
-  if (p->grp_tiles == nullptr || p->grp_num_tiles == nullptr || p->out_f32 == nullptr || p->K2 != 0 || max_tiles < 1 || p->N % 4 != 0)
-    return cudaErrorInvalidValue;
+  if (p->grp_tiles == nullptr || p->grp_num_tiles == nullptr || p->K2 != 0 || max_tiles < 1 || p->N % 4 != 0) return cudaErrorInvalidValue;
+  if (p->out_bf16 == nullptr ? p->out_f32 == nullptr : (p->N % 64 != 0 || p->out_stride % 8 != 0)) return cudaErrorInvalidValue;
   if (bn == 64) return launch_grouped<64>(maps, *p, max_tiles, num_sms, stream);
   if (bn == 128) return launch_grouped<128>(maps, *p, max_tiles, num_sms, stream);
   if (bn == 256) return launch_grouped<256>(maps, *p, max_tiles, num_sms, stream);

@@ -51,8 +51,10 @@ extern "C" cudaError_t nrl_gemm_tc_fp8(const CUtensorMap* maps, const nrl::tc::T
 // batched K-major x K-major GEMM, bf16 out; maps = {A, B, D} 3D (tma_host.h make_tma_3d), B box rows = bn / cg
 extern "C" cudaError_t nrl_gemm_tc_batched(const CUtensorMap* maps, const nrl::tc::TcParams* p, int cg, int bn, int num_sms,
                                            cudaStream_t stream);
-// grouped K-major x K-major GEMM with the float32 epilogue (cta_group 1); maps = {A [rows, K] box {128, 64}, B [experts * N, K]
-// box {bn, 64}}; out_f32 [rows, N]; p->N = columns per expert; max_tiles bounds the table's length (grid size)
+// grouped K-major x K-major GEMM (cta_group 1); maps = {A [rows, K] box {128, 64}, B [experts * N, K] box {bn, 64}};
+// p->N = columns per expert; max_tiles bounds the table's length (grid size).  Output: out_f32 [rows, N], or, when out_bf16 is
+// set, the SwiGLU of the columns: B rows interleaved per 32 features ([32 gate | 32 up], N % 64 == 0), out_bf16 [rows, N / 2]
+// (row stride out_stride, a multiple of 8) = silu(gate) * up.
 extern "C" cudaError_t nrl_gemm_tc_grouped(const CUtensorMap* maps, const nrl::tc::TcParams* p, int bn, int max_tiles, int num_sms,
                                            cudaStream_t stream);
 extern "C" cudaError_t nrl_gemm_tc(const CUtensorMap* maps, const nrl::tc::TcParams* p, int cg, int bn, int a_mn, int b_mn,

@@ -1,5 +1,6 @@
 """Op layer of hybrid (attention + recurrent-state) decoders: thin, launch-counting wrappers over the sm_100a kernels of
-``csrc/stream_ops.cu``, ``csrc/recurrent.cu`` and ``csrc/attention_window.cu``.
+``csrc/stream_ops.cu``, ``csrc/recurrent.cu``, ``csrc/attention_window.cu`` / ``attention_window_mma.cu`` and ``csrc/moe.cu``
+(with the grouped form of ``csrc/gemm_tc.cu``).
 
 All of them take the step plan of ``_C.StepScheduler.plan`` (entries = runs of consecutive tokens of one sequence) and
 work on packed ``[tokens, ...]`` tensors; recurrent state and convolution taps live in per-sequence slots, keys and values
@@ -109,22 +110,34 @@ def moe_route(router, router_bias, top, gu=None, ff=0, act=None, ids=None, wts=N
     _ext().moe_route(router, router_bias, top, gu, ff, act, ids, wts)
 
 
-def moe_grouped_ffn(h, ids, wts, w_gate_up, w_down, experts, ff, out):
+def interleave_gate_up(gate, up):
+    """Rows of one expert's gate and up matrices [ff, W] interleaved per 32 features ([32 gate | 32 up] ...): the layout the
+    grouped GEMM's SwiGLU epilogue expects (``ff % 32 == 0``)."""
+    import torch
+    ff, W = gate.shape
+    return torch.stack([gate.view(ff // 32, 32, W), up.view(ff // 32, 32, W)], 1).reshape(2 * ff, W)
+
+
+def moe_grouped_ffn(h, ids, wts, w_gate_up, w_down, experts, ff, out, fused_act: bool = False):
     """Expert feed-forwards of a routed batch on the grouped tcgen05 GEMM.  ``h`` bf16 [T, W]; ``ids`` / ``wts`` [T, top] from
-    ``moe_route``; ``w_gate_up`` bf16 [experts * 2 ff, W] (per expert its gate rows, then its up rows); ``w_down`` bf16
-    [experts * W, ff]; ``out`` float [T, W] = sum_k wts[t, k] * expert_k(h[t]).  Six launches, none depends on the routing."""
+    ``moe_route``; ``w_gate_up`` bf16 [experts * 2 ff, W] (per expert its gate rows, then its up rows; ``fused_act``: interleaved
+    per 32 features by ``interleave_gate_up``, the SwiGLU is then formed in the GEMM's epilogue); ``w_down`` bf16
+    [experts * W, ff]; ``out`` float [T, W] = sum_k wts[t, k] * expert_k(h[t]).  No launch depends on the routing."""
     import torch
     T, W = h.shape
     R = ids.numel()
     ext = _ext()
-    native._count(6)
+    native._count(5 if fused_act else 6)
     slot_of, row_token, _seg, tiles, num_tiles = ext.moe_plan(ids, experts, 128)
     xp = torch.empty(R, W, dtype=h.dtype, device=h.device)
     ext.gather_rows(h, row_token, xp)
-    gu = torch.empty(R, 2 * ff, dtype=torch.float32, device=h.device)
-    ext.gemm_tc_grouped(xp, w_gate_up, gu, tiles, num_tiles)
     act = torch.empty(R, ff, dtype=h.dtype, device=h.device)
-    ext.swiglu_rows(gu, act)
+    if fused_act:
+        ext.gemm_tc_grouped(xp, w_gate_up, None, tiles, num_tiles, 0, act)
+    else:
+        gu = torch.empty(R, 2 * ff, dtype=torch.float32, device=h.device)
+        ext.gemm_tc_grouped(xp, w_gate_up, gu, tiles, num_tiles)
+        ext.swiglu_rows(gu, act)
     y = torch.empty(R, W, dtype=torch.float32, device=h.device)
     ext.gemm_tc_grouped(act, w_down, y, tiles, num_tiles)
     ext.moe_combine(y, slot_of, wts, out)

@@ -12,6 +12,11 @@ step in a per-sequence slot) and it gives chunked prefill and continuous batchin
   input, gates, decays, feed-forward up) is one GEMM, and every projection that writes the stream (attention out,
   state-space out, feed-forward down) is one GEMM over the concatenated activations, mixer scales folded into the
   activations;
+* two kinds of residual stream (``StreamSpec.kind``): "depth_weighted" (one norm per layer, mixers and feed-forward side by
+  side, the stream a learned weighted sum of all earlier results) and "sandwich" (a norm before and after each sublayer, a
+  sigmoid gate on the sublayer's result; the mixer and the feed-forward are two stages, each with its own pair of fused
+  matrices); a mixture-of-experts feed-forward runs only the chosen experts, rows sorted by expert through a grouped
+  tcgen05 GEMM (float32 serving: dense form on cuBLAS);
 * the residual stream, its depth-weighted average, norms, scores, softmax, decays and recurrent state are float32 in both
   serving modes; ``dtype="bf16"`` keeps GEMM operands and KV pages in bf16 (fp32 accumulation, fp32 GEMM results),
   ``dtype="fp32"`` keeps everything in float32 with TF32 off;
@@ -241,8 +246,13 @@ class HybridSampler:
                 # grouped GEMM, [experts * 2 ff, W] (gate rows, then up rows) and [experts * W, ff]
                 L.router_col = add_in(p + "mlp.router")
                 L.router_bias = self._f(p + "mlp.router.b") if self.lm.has_tensor(p + "mlp.router.b") else None
-                L.w_gate_up = torch.cat([self._t(f"{p}mlp.e{e}.{n}").to(device=dev, dtype=wd) for e in range(spec.experts)
-                                         for n in ("gate", "up")], 0).contiguous()
+                if spec.ff % 32 == 0:                      # gate / up rows interleaved: the SwiGLU is formed in the GEMM's epilogue
+                    L.w_gate_up = torch.cat([hy.interleave_gate_up(self._t(f"{p}mlp.e{e}.gate").to(device=dev, dtype=wd),
+                                                                   self._t(f"{p}mlp.e{e}.up").to(device=dev, dtype=wd))
+                                             for e in range(spec.experts)], 0).contiguous()
+                else:
+                    L.w_gate_up = torch.cat([self._t(f"{p}mlp.e{e}.{n}").to(device=dev, dtype=wd) for e in range(spec.experts)
+                                             for n in ("gate", "up")], 0).contiguous()
                 L.w_down = torch.cat([self._t(f"{p}mlp.e{e}.down").to(device=dev, dtype=wd) for e in range(spec.experts)], 0).contiguous()
             elif spec.ff_kind == "moe":                   # dense form: router, then per expert its gate rows and its up rows
                 L.router_col = add_in(p + "mlp.router")
@@ -459,7 +469,7 @@ class HybridSampler:
         wts = torch.empty(T, spec.top, dtype=torch.float32, device=dev)
         hy.moe_route(U[:, rc:rc + E], L.router_bias, spec.top, ids=ids, wts=wts)
         y = torch.empty(T, self.cfg.width, dtype=torch.float32, device=dev)
-        hy.moe_grouped_ffn(h, ids, wts, L.w_gate_up, L.w_down, E, spec.ff, y)
+        hy.moe_grouped_ffn(h, ids, wts, L.w_gate_up, L.w_down, E, spec.ff, y, fused_act=spec.ff % 32 == 0)
         if o is None:
             return y
         native._count()

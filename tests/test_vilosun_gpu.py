@@ -498,7 +498,7 @@ def test_trace_runner_replays_a_mixed_trace(tmp_path):
 
 # ---- mixture of experts on the grouped GEMM ---------------------------------------------------------------------------
 @pytest.mark.parametrize("T,E,top,W,ff", [(1, 4, 2, 64, 64), (37, 5, 2, 128, 72), (300, 7, 3, 64, 136), (513, 3, 1, 192, 64),
-                                          (260, 2, 2, 64, 8), (700, 40, 4, 64, 64)])
+                                          (260, 2, 2, 64, 8), (700, 40, 4, 64, 64), (400, 5, 2, 64, 96), (300, 3, 2, 128, 160)])
 def test_grouped_expert_feed_forward(T, E, top, W, ff):
     """Rows sorted by expert through the grouped tensor-core GEMM against a loop over tokens; experts without tokens, experts
     whose rows end inside a tile, more tiles than experts."""
@@ -515,6 +515,11 @@ def test_grouped_expert_feed_forward(T, E, top, W, ff):
     hy.moe_route(z.cuda(), None, top, ids=ids, wts=wts)
     out = torch.empty(T, W, device="cuda")
     hy.moe_grouped_ffn(h.cuda(), ids, wts, wgu.cuda(), wdn.cuda(), E, ff, out)
+    if ff % 32 == 0:                                        # the SwiGLU formed in the first GEMM's epilogue gives the same result
+        inter = torch.cat([hy.interleave_gate_up(wgu[e * 2 * ff:e * 2 * ff + ff], wgu[e * 2 * ff + ff:(e + 1) * 2 * ff]) for e in range(E)], 0)
+        fused = torch.empty(T, W, device="cuda")
+        hy.moe_grouped_ffn(h.cuda(), ids, wts, inter.cuda().contiguous(), wdn.cuda(), E, ff, fused, fused_act=True)
+        assert (fused - out).abs().max().item() < 2e-3 * max(1.0, out.abs().max().item())
     want = torch.zeros(T, W, dtype=torch.float64)
     hd = h.double()
     for e in range(E):
