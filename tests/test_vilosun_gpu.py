@@ -471,6 +471,23 @@ def test_greedy_generation_through_the_engine_entry_point(tmp_path, dtype):
     release_native_engine(model)
 
 
+def test_sampled_generation_is_seeded_and_replays_graphs(tmp_path):
+    """Temperature / top-p sampling through the same entry point: rows are reproducible per seed, differ across seeds and
+    samples, stay inside the vocabulary; decode steps of a fixed batch replay a CUDA graph."""
+    from nanorlhf_b200.models.registry import load_model
+    from nanorlhf_b200.sampler.engine import generate, get_native_engine, release_native_engine
+    cfg, W = _model("mixed", dtype="bf16")
+    model = load_model(_save(tmp_path, cfg, W), torch_dtype=torch.bfloat16, device="cuda")
+    prompts = [_tokens(cfg, n, 40 + n) for n in (5, 12)]
+    a = generate(2, model, _Tok(), prompts, 1.0, 20, top_p=0.9, seed=7, rollout_dtype="bf16").cpu()
+    b = generate(2, model, _Tok(), prompts, 1.0, 20, top_p=0.9, seed=7, rollout_dtype="bf16").cpu()
+    c = generate(2, model, _Tok(), prompts, 1.0, 20, top_p=0.9, seed=8, rollout_dtype="bf16").cpu()
+    assert a.shape == (4, 20) and torch.equal(a, b) and not torch.equal(a, c)
+    assert not torch.equal(a[0], a[1]) and int(a.min()) >= 0 and int(a.max()) < cfg["vocab"]
+    assert get_native_engine(model, rollout_dtype="bf16").stats["graph_replays"] > 0
+    release_native_engine(model)
+
+
 def test_trace_runner_replays_a_mixed_trace(tmp_path):
     """bin/trace_run as a subprocess: portions beside single tokens, a pool that forces pages and slots to be reused."""
     import numpy as np
