@@ -125,3 +125,13 @@ def test_oracle_router_weights():
         a = O.silu(O.lin(W[f"l0.mlp.e{e}.gate"], h)) * O.lin(W[f"l0.mlp.e{e}.up"], h)
         want += p[:, e:e + 1] * O.lin(W[f"l0.mlp.e{e}.down"], a)
     assert (full - want).abs().max() < 1e-9
+
+
+def test_gate_up_rows_interleave_per_32_features():
+    """The layout the grouped GEMM's SwiGLU epilogue reads: [32 gate rows | 32 up rows] per block of 32 features."""
+    from nanorlhf_b200.ops.hybrid import interleave_gate_up
+    gate = torch.arange(64 * 3, dtype=torch.float32).view(64, 3)
+    w = interleave_gate_up(gate, -gate)
+    assert w.shape == (128, 3)
+    assert torch.equal(w[:32], gate[:32]) and torch.equal(w[32:64], -gate[:32])
+    assert torch.equal(w[64:96], gate[32:]) and torch.equal(w[96:], -gate[32:])

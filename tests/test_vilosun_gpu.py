@@ -95,6 +95,14 @@ SHAPES = {
     # long chunks (several pages), many experts, a width that is no multiple of 64
     "long_chunk": dict(layers=("attention", "attention"), width=40, attn=dict(heads=4, kv_heads=4, dim=16, vdim=16, size=200),
                        moe=dict(ff=8, experts=17, top=3), chunk=[200, 48], v_mix=[False, False]),
+    # sizes of a small real model: grouped key/value heads, three norm groups, four taps, a layer that does not blend
+    "medium": dict(vocab=1000, width=384, layers=("delta", "attention", "attention", "delta", "attention"), groups=3, embed_scale=12.0,
+                   logit_scale=0.3, bigram=(997, 131, 71), attn=dict(heads=6, kv_heads=2, dim=32, vdim=48, conv=4, size=96, scale=0.2),
+                   v_mix=[True, False, True], delta=dict(heads=6, kv_heads=3, dim=32, vdim=48, conv=4), moe=dict(ff=96, experts=8, top=2)),
+    # a width that is no multiple of 64, five heads, head sizes off the tensor-core tile, many experts, five norm groups
+    "odd": dict(vocab=333, width=200, layers=("attention", "delta", "attention-"), groups=5, embed_scale=2.0, logit_scale=1.5,
+                bigram=(50, 3, 1), attn=dict(heads=5, kv_heads=5, dim=24, vdim=40, conv=2, size=33, scale=0.25), v_mix=[True, True],
+                delta=dict(heads=4, kv_heads=1, dim=40, vdim=24, conv=3), moe=dict(ff=40, experts=20, top=5)),
 }
 
 
